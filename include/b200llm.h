@@ -431,14 +431,25 @@ int b200_lm_head_topk_sample(b200_decoder_t *dec, const void *hidden, const void
 typedef enum {
     B200_MIXER_ATTN_CHUNKED = 1, /* softmax attention, no rotation, block-diagonal causal mask, optional sink, sigmoid output gate      */
     B200_MIXER_GLA = 2,          /* gated linear attention: per-key-channel decay, fp32 matrix state per head                         */
-    B200_MIXER_LATENT = 3        /* latent attention: keys and values are up-projections of ONE cached low-rank row per position, plus
+    B200_MIXER_LATENT = 3,       /* latent attention: keys and values are up-projections of ONE cached low-rank row per position, plus
                                     one rotated key part shared by the heads; sliding window, optional sink, sigmoid output gate      */
+    B200_MIXER_ATTN_SCORED = 4,  /* grouped-query attention over paged keys [dim] and values [vdim] whose parts are all options: biases,
+                                    per-head q/k RMS norm, interleaved rotation of the first rot_dims dimensions, sliding window, a
+                                    logarithmic distance penalty, weights by softmax or by an un-normalised sigmoid, output gate      */
+    B200_MIXER_DELTA = 5,        /* gated delta rule: short causal convolutions, unit q/k, a decay per head and key channel, fp32
+                                    matrix state per head that is corrected towards the value before it is read                      */
+    B200_MIXER_MLSTM = 6         /* matrix memory with exponential input gate, sigmoid forget gate and a running maximum (mLSTM)     */
 } b200_mixer_kind_t;
+typedef enum { B200_ATTN_SOFTMAX = 0, B200_ATTN_SIGMOID = 1 } b200_attn_weight_t;
 typedef enum { B200_MLP_NONE = 0, B200_MLP_MOE = 1, B200_MLP_DENSE = 2 } b200_mlp_kind_t;
-typedef enum { B200_ACT_RELU2 = 0, B200_ACT_SILU = 1, B200_ACT_GELU_TANH = 2 } b200_act_t;
+typedef enum { B200_ACT_RELU2 = 0, B200_ACT_SILU = 1, B200_ACT_GELU_TANH = 2, B200_ACT_RELU = 3 } b200_act_t;
 typedef enum {
     B200_NORM_RMS_POST = 0,      /* x += rmsnorm(sublayer(x)) * g                                                                     */
-    B200_NORM_DYT_PRE_POST = 1   /* x += ls * dyt_b(sublayer(dyt_a(x))), dyt(v) = tanh(alpha v) * w + b: no mean, no variance         */
+    B200_NORM_DYT_PRE_POST = 1,  /* x += ls * dyt_b(sublayer(dyt_a(x))), dyt(v) = tanh(alpha v) * w + b: no mean, no variance         */
+    B200_NORM_LN_PARALLEL = 2    /* y = layernorm(x) (weight and bias, packed [w | b] in pre1);  x += mixer(y) + ff(y): ONE norm, both
+                                    sublayers read it.  Their input projections are one matrix (w_in: mixer rows, side mixer rows,
+                                    then the feed-forward's gate rows and up rows) and so are their output projections (w_out
+                                    [width, mixer columns | side mixer columns | expert_ff]); w_up / w_down stay NULL                 */
 } b200_norm_kind_t;
 typedef enum {
     B200_ROUTE_SIGMOID = 0,      /* scores = sigmoid(logits), the chosen scores are the weights, applied to the expert's INPUT        */
@@ -455,10 +466,14 @@ typedef struct {
     int max_pages_per_seq;
     float embed_scale;  /* x = embedding[token] * embed_scale; 0 reads as 1                                                           */
     float logit_softcap;/* logits <- cap * tanh(logits / cap); 0: none                                                                */
-    int final_norm;     /* b200_norm_kind_t of the model's last norm (RMS_POST: plain RMS norm; DYT: packed [w | b | alpha])          */
+    int final_norm;     /* b200_norm_kind_t of the model's last norm (RMS_POST: plain RMS norm; DYT: packed [w | b | alpha];
+                           LN_PARALLEL: layer norm, packed [w | b])                                                                  */
+    int loop_start, loop_stop, loop_times; /* loop_times > 0: layers [loop_start, loop_stop) run loop_times times in a row with the same
+                           weights, every pass with a cache and state of its own (b200_hybrid_set_loop gives the entry step's weights);
+                           0: every layer runs once                                                                                  */
 } b200_hybrid_config_t;
 
-typedef struct {
+typedef struct b200_hybrid_layer_s {
     int mixer;          /* b200_mixer_kind_t                                                                                          */
     int heads, kv_heads, dim, vdim;
     float scale;        /* ATTN, LATENT: score scale                                                                                  */
@@ -502,6 +517,28 @@ typedef struct {
     const float *ls1, *ls2;       /* DYT_PRE_POST: [width] layer scale, or NULL                                                       */
     const float *route_bias;      /* MOE, SOFTMAX: [experts + identity] added to the scores for the choice only, or NULL              */
     const float *b_up, *b_down;   /* DENSE: [expert_ff], [width], or NULL                                                             */
+    /* ---- ATTN_SCORED (also rot_dims / rot_base: pairs (2i, 2i+1) of the first rot_dims dimensions of every q and k head; window;
+     *      q_norm / k_norm [dim]: RMS norm per head, one weight vector shared by the heads, or NULL; w_in rows q (heads*dim), k
+     *      (kv_heads*dim), v (kv_heads*vdim), gate (heads*vdim, if out_gate)) */
+    int attn_weight;              /* b200_attn_weight_t: SOFTMAX over the visible keys, or SIGMOID: sigmoid(score + head_bias), not normalised */
+    int out_gate;                 /* 1: the concatenated heads are multiplied by sigmoid(gate rows . input)                           */
+    const float *head_bias;       /* SIGMOID: [heads] added to the score, or NULL                                                     */
+    const float *dist_r1, *dist_r2; /* [heads] each or NULL: score(i, j) -= r1 * ln(1 + r2 * (i - j))                                 */
+    const float *b_in, *b_out;    /* [rows of w_in] added to the input projection, [width] added to the output projection, or NULL    */
+    /* ---- DELTA: w_in rows q, k (kv_heads*dim each), v (heads*vdim), step (heads), decay-in (decay_rank), gate-in (gate_rank);
+     *      w_decay [heads*dim, decay_rank], decay_bias [heads*dim]: decay = exp(-exp(a_log[head]) * softplus(w_decay . decay-in + bias));
+     *      w_gate2 [heads*vdim, gate_rank]: output gate sigmoid(w_gate2 . gate-in); out_norm [vdim] */
+    int conv;                     /* taps of the causal per-channel convolution on q, k and v (followed by silu)                      */
+    int gate_rank;
+    const float *conv_w;          /* [2*kv_heads*dim + heads*vdim, conv]: channels in the order q, k, v; the last tap is the current token's */
+    const float *a_log;           /* [heads]                                                                                          */
+    const void *w_gate2;
+    /* ---- MLSTM: w_in rows q, k (heads*dim each), v, gate (heads*vdim each), input gate, forget gate (heads each); b_in carries the gates'
+     *      biases; out_norm [heads*vdim] */
+    float gate_cap;               /* log gates: i = cap * tanh(z_i / cap), f = logsigmoid(cap * tanh(z_f / cap))                      */
+    /* ---- a second mixer beside the first: both read the same input, result = mix_scale * mixer + side_scale * side mixer */
+    const struct b200_hybrid_layer_s *side; /* only its mixer fields are read (LN_PARALLEL layers); NULL: none                        */
+    float mix_scale, side_scale;  /* 0 reads as 1                                                                                     */
 } b200_hybrid_layer_t;
 
 typedef struct {
@@ -520,16 +557,23 @@ void b200_hybrid_destroy(b200_hybrid_t *m);
 int b200_hybrid_set_layer(b200_hybrid_t *m, int layer, const b200_hybrid_layer_t *w);
 /* embedding [vocab, width], lm_head [vocab, width] (engine dtype), final_norm fp32 [width] (DYT: packed [w | b | alpha]) */
 int b200_hybrid_set_io(b200_hybrid_t *m, const void *embedding, const float *final_norm, const void *lm_head);
+/* The looped block's entry step, run before the first layer of every pass t = 0 .. loop_times - 1:  x <- w_entry [x ; x0] + step[t], with
+ * x0 the embedding output.  w_entry [width, 2*width] (engine dtype, x's columns first), step fp32 [loop_times, width]. */
+int b200_hybrid_set_loop(b200_hybrid_t *m, const void *w_entry, const float *step);
+/* Layer runs of one forward call: num_layers + (loop_times - 1) * (loop_stop - loop_start). */
+int b200_hybrid_num_runs(const b200_hybrid_t *m);
 size_t b200_hybrid_scratch_bytes(const b200_hybrid_t *m);
 int b200_hybrid_set_scratch(b200_hybrid_t *m, void *ptr, size_t bytes);
-/* Key/value pool: per attention layer K [num_pages, kv_heads, B200_KV_PAGE_SIZE, dim] then V; per latent layer with a cache of its own
- * [num_pages, B200_KV_PAGE_SIZE, kv_rank + rot_dim] (latent row, then the rotated key part), of the engine dtype (layers may differ in
- * size; each starts 256-byte aligned).  State pool: per recurrent layer fp32 [num_slots, heads, dim, vdim].  Caller-owned. */
+/* Key/value pool: per attention layer K [num_pages, kv_heads, B200_KV_PAGE_SIZE, dim] then V ([.., vdim] for ATTN_SCORED); per latent layer
+ * with a cache of its own [num_pages, B200_KV_PAGE_SIZE, kv_rank + rot_dim] (latent row, then the rotated key part), of the engine dtype
+ * (layers may differ in size; each starts 256-byte aligned).  State pool: per recurrent layer fp32 [num_slots, heads, dim, vdim]; DELTA
+ * adds the convolutions' last conv - 1 inputs [num_slots, conv - 1, channels], MLSTM the normaliser [num_slots, heads, dim] and the running
+ * maximum [num_slots, heads].  A layer that runs several times (loop) owns one such region per run.  Caller-owned. */
 size_t b200_hybrid_kv_pool_bytes(const b200_hybrid_t *m, int num_pages);
 size_t b200_hybrid_state_pool_bytes(const b200_hybrid_t *m, int num_slots);
 int b200_hybrid_set_pools(b200_hybrid_t *m, void *kv_pool, int num_pages, void *state_pool, int num_slots);
-/* logits: DEVICE fp32 [n_want, vocab] (may be NULL when n_want == 0).  layer_trace (optional): DEVICE fp32 [num_layers, n_tokens, width],
- * the residual stream after every layer.  Stream-ordered, allocation-free; the host arrays may be reused when the call returns. */
+/* logits: DEVICE fp32 [n_want, vocab] (may be NULL when n_want == 0).  layer_trace (optional): DEVICE fp32 [layer runs, n_tokens, width],
+ * the residual stream after every layer run.  Stream-ordered, allocation-free; the host arrays may be reused when the call returns. */
 int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *batch, float *logits, float *layer_trace, b200_stream_t stream);
 
 /* ---- the mechanisms, one launcher each (the engine calls exactly these) */

@@ -62,7 +62,7 @@ class HybridConfig(C.Structure):
     """b200_hybrid_config_t (include/b200llm.h)."""
     _fields_ = [("width", C.c_int), ("vocab", C.c_int), ("num_layers", C.c_int), ("dtype", C.c_int), ("norm_eps", C.c_float),
                 ("max_tokens", C.c_int), ("max_seqs", C.c_int), ("max_pages_per_seq", C.c_int), ("embed_scale", C.c_float),
-                ("logit_softcap", C.c_float), ("final_norm", C.c_int)]
+                ("logit_softcap", C.c_float), ("final_norm", C.c_int), ("loop_start", C.c_int), ("loop_stop", C.c_int), ("loop_times", C.c_int)]
 
 
 class HybridLayer(C.Structure):
@@ -78,7 +78,11 @@ class HybridLayer(C.Structure):
                 ("kv_from", C.c_int), ("route", C.c_int), ("identity", C.c_int), ("gated", C.c_int),
                 ("kv_norm", C.c_void_p), ("w_uk_t", C.c_void_p), ("w_uv", C.c_void_p), ("pre1", C.c_void_p), ("post1", C.c_void_p),
                 ("pre2", C.c_void_p), ("post2", C.c_void_p), ("ls1", C.c_void_p), ("ls2", C.c_void_p), ("route_bias", C.c_void_p),
-                ("b_up", C.c_void_p), ("b_down", C.c_void_p)]
+                ("b_up", C.c_void_p), ("b_down", C.c_void_p),
+                ("attn_weight", C.c_int), ("out_gate", C.c_int), ("head_bias", C.c_void_p), ("dist_r1", C.c_void_p), ("dist_r2", C.c_void_p),
+                ("b_in", C.c_void_p), ("b_out", C.c_void_p), ("conv", C.c_int), ("gate_rank", C.c_int), ("conv_w", C.c_void_p),
+                ("a_log", C.c_void_p), ("w_gate2", C.c_void_p), ("gate_cap", C.c_float), ("side", C.c_void_p), ("mix_scale", C.c_float),
+                ("side_scale", C.c_float)]
 
 
 class HybridBatch(C.Structure):
@@ -87,11 +91,12 @@ class HybridBatch(C.Structure):
                 ("seq_pos0", C.c_void_p), ("seq_slot", C.c_void_p), ("block_table", C.c_void_p), ("want_rows", C.c_void_p)]
 
 
-MIXER_ATTN_CHUNKED, MIXER_GLA, MIXER_LATENT = 1, 2, 3
+MIXER_ATTN_CHUNKED, MIXER_GLA, MIXER_LATENT, MIXER_ATTN_SCORED, MIXER_DELTA, MIXER_MLSTM = 1, 2, 3, 4, 5, 6
+ATTN_SOFTMAX, ATTN_SIGMOID = 0, 1
 MLP_NONE, MLP_MOE, MLP_DENSE = 0, 1, 2
-NORM_RMS_POST, NORM_DYT_PRE_POST = 0, 1
+NORM_RMS_POST, NORM_DYT_PRE_POST, NORM_LN_PARALLEL = 0, 1, 2
 ROUTE_SIGMOID, ROUTE_SOFTMAX = 0, 1
-ACT_RELU2, ACT_SILU, ACT_GELU_TANH = 0, 1, 2
+ACT_RELU2, ACT_SILU, ACT_GELU_TANH, ACT_RELU = 0, 1, 2, 3
 (PLAN_MIXED_IDS, PLAN_MIXED_STARTS, PLAN_MIXED_POS0, PLAN_MIXED_SLOTS, PLAN_MIXED_REQUESTS, PLAN_MIXED_BLOCK_TABLE,
  PLAN_MIXED_SAMPLE_ROWS) = range(16, 23)
 
@@ -181,6 +186,8 @@ SIGNATURES = {
     "b200_hybrid_destroy": [_P],
     "b200_hybrid_set_layer": [_P, _I, C.POINTER(HybridLayer)],
     "b200_hybrid_set_io": [_P, _P, _P, _P],
+    "b200_hybrid_set_loop": [_P, _P, _P],
+    "b200_hybrid_num_runs": [_P],
     "b200_hybrid_scratch_bytes": [_P],
     "b200_hybrid_set_scratch": [_P, _P, _SZ],
     "b200_hybrid_kv_pool_bytes": [_P, _I],
@@ -196,6 +203,11 @@ SIGNATURES = {
     "b200_latent_prep_paged": [_P, _I, _I, _I, _P, _P, _P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "b200_latent_attention_paged": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "b200_latent_attention_tiles_paged": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _I, _I, _P],
+    "b200_scored_attn_prep_paged": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "b200_scored_attention_paged": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "b200_scored_attention_tiles_paged": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _F, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "b200_delta_rule_recurrent": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "b200_mlstm_recurrent": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "b200_batcher_set_state_slots": [_P, _I],
     "b200_batcher_free_slots": [_P],
     "b200_batcher_set_chunk": [_P, _I],

@@ -347,6 +347,7 @@ __device__ __forceinline__ float act_apply(float v, int act) {
         return r * r;
     }
     if (act == B200_ACT_SILU) return v / (1.0f + expf(-v));
+    if (act == B200_ACT_RELU) return fmaxf(v, 0.0f);
     const float c = 0.7978845608028654f;  // sqrt(2/pi)
     return 0.5f * v * (1.0f + tanhf(c * (v + 0.044715f * v * v * v)));
 }

@@ -403,10 +403,101 @@ int launch_proj_f32(int x_dtype, const void *x, int ldx, int w_dtype, const void
     return cuda_status("proj_f32 launch");
 }
 
-struct LayerPlan {
+// ---- layers of one norm whose sublayers all read it (B200_NORM_LN_PARALLEL)
+// x[t, :] = table[id] * scale, and its copy of the engine dtype at h2[t * h2_ld + :] (optional)
+template <typename T>
+__global__ void embed_rows_kernel(const int *__restrict__ ids, const T *__restrict__ table, float *__restrict__ x, T *__restrict__ h2, int h2_ld,
+                                  int width, int vocab, float scale) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // the host has refused ids outside the vocabulary
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = Elem<T>::to_f(table[(size_t)id * width + c]) * scale;
+        x[(size_t)t * width + c] = v;
+        if (h2) h2[(size_t)t * h2_ld + c] = Elem<T>::from_f(v);
+    }
+}
+
+// The residual step of such a layer and whatever the next layer run reads, in one kernel:
+//   v = (replace ? y32[t, :] : x[t, :] + y[t, :]) + bias;   x[t, :] = v;   trace[t, :] = v;
+//   h_out[t * h_ld + :] = ln ? T((v - mean) * rsqrt(var + eps) * w + b) : T(v)        (ln packed [w | b]; var = mean of squared deviations)
+// y, y32, bias, trace and h_out are optional.  The row waits in shared memory between the passes: mean first, then the deviations.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ln_residual_kernel(float *__restrict__ x, const T *__restrict__ y, const float *__restrict__ y32, const float *__restrict__ bias, int replace,
+                   const float *__restrict__ ln, float eps, int width, T *__restrict__ h_out, int h_ld, float *__restrict__ trace) {
+    extern __shared__ __align__(16) float row[];  // [width]
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    float sum = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = replace ? y32[(size_t)t * width + c] : x[(size_t)t * width + c] + (y ? Elem<T>::to_f(y[(size_t)t * width + c]) : 0.0f);
+        if (bias) v += bias[c];
+        if (replace || y || bias) x[(size_t)t * width + c] = v;
+        if (trace) trace[(size_t)t * width + c] = v;
+        row[c] = v;
+        sum += v;
+    }
+    if (!h_out) return;
+    if (!ln) {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) h_out[(size_t)t * h_ld + c] = Elem<T>::from_f(row[c]);  // (a thread reads what it wrote)
+        return;
+    }
+    const float mean = block_sum(sum, red) / (float)width;
+    float sq = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float d = row[c] - mean;
+        sq = fmaf(d, d, sq);
+    }
+    const float inv = rsqrtf(block_sum(sq, red) / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) h_out[(size_t)t * h_ld + c] = Elem<T>::from_f(fmaf((row[c] - mean) * inv, ln[c], ln[width + c]));
+}
+
+// out[r * out_ld + c] = T(act(in[r * in_ld + gate_col + c]) * in[r * in_ld + up_col + c]): the gated feed-forward's inner row, read from
+// and written into rows that other sublayers share
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_act_strided_kernel(const T *__restrict__ in, int in_ld, int gate_col, int up_col, T *__restrict__ out, int out_ld, int rows, int inner, int act) {
+    const size_t n = (size_t)rows * inner;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / inner;
+        const int c = (int)(i - r * inner);
+        const T *src = in + r * in_ld;
+        out[r * out_ld + c] = Elem<T>::from_f(act_apply(Elem<T>::to_f(src[gate_col + c]), act) * Elem<T>::to_f(src[up_col + c]));
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+final_ln_rows_kernel(const float *__restrict__ x, const int *__restrict__ rows, const float *__restrict__ p, float eps, float *__restrict__ out,
+                     T *__restrict__ out_t, int width) {
+    __shared__ float red[33];
+    const int i = blockIdx.x;
+    const float *xr = x + (size_t)rows[i] * width;
+    float sum = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) sum += xr[c];
+    const float mean = block_sum(sum, red) / (float)width;
+    float sq = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) sq = fmaf(xr[c] - mean, xr[c] - mean, sq);
+    const float inv = rsqrtf(block_sum(sq, red) / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = fmaf((xr[c] - mean) * inv, p[c], p[width + c]);
+        out[(size_t)i * width + c] = v;
+        if (out_t) out_t[(size_t)i * width + c] = Elem<T>::from_f(v);
+    }
+}
+
+// where one mixer of one layer run keeps what it remembers
+struct MixerPlan {
+    size_t k_off = 0, v_off = 0;      // attention kinds: byte offsets into the kv pool (set by set_pools); LATENT: k_off of the rows it reads
+    size_t state_off = 0;             // recurrent kinds: byte offset of the matrix state in the state pool
+    size_t aux_off = 0, aux2_off = 0; // DELTA: the convolutions' inputs;  MLSTM: the normaliser and the running maximum
+};
+struct LayerPlan : MixerPlan {
     int n_in = 0;                     // rows of the fused input projection
-    size_t k_off = 0, v_off = 0;      // ATTN: byte offsets into the kv pool (set by set_pools); LATENT: k_off of the rows this layer reads
-    size_t state_off = 0;             // GLA: byte offset into the state pool
+    int layer = 0;                    // which layer this run executes
+    int entry = -1;                   // >= 0: the run opens pass `entry` of the looped block (the entry step comes first)
+    MixerPlan side;                   // the second mixer beside the first
 };
 
 }  // namespace b200
@@ -417,9 +508,10 @@ struct b200_hybrid {
     b200_hybrid_config_t cfg;
     std::vector<b200_hybrid_layer_t> layers;
     std::vector<char> layer_set;
-    std::vector<LayerPlan> plan;
-    const void *embedding = nullptr, *lm_head = nullptr;
-    const float *final_norm = nullptr;
+    std::vector<LayerPlan> plan;                // one per layer RUN (a looped layer runs several times, each with a cache of its own)
+    std::vector<b200_hybrid_layer_t> sides;     // the engine's copies of the second mixers (layers[i].side points here)
+    const void *embedding = nullptr, *lm_head = nullptr, *w_entry = nullptr;
+    const float *final_norm = nullptr, *loop_step = nullptr;
     char *kv_pool = nullptr, *state_pool = nullptr;
     int num_pages = 0, num_slots = 0;
     // scratch carve-up
@@ -427,7 +519,8 @@ struct b200_hybrid {
     float *x = nullptr, *f32a = nullptr, *f32b = nullptr, *xn = nullptr;
     void *h = nullptr, *proj = nullptr, *mix = nullptr, *mix2 = nullptr, *y = nullptr, *xg = nullptr, *u = nullptr, *yrows = nullptr, *us = nullptr,
          *ys = nullptr, *lqn = nullptr, *lqr = nullptr, *lql = nullptr, *lol = nullptr, *lov = nullptr;
-    float *lpart = nullptr;
+    float *lpart = nullptr, *rec = nullptr, *f32c = nullptr;
+    void *cat = nullptr, *xc = nullptr;
     int *meta = nullptr, *moe_i = nullptr;
     float *moe_f = nullptr;
     std::vector<int> host_meta;
@@ -436,8 +529,24 @@ struct b200_hybrid {
 namespace {
 
 struct Carve {
-    size_t x, f32a, f32b, xn, h, proj, mix, y, xg, u, yrows, us, ys, lqn, lqr, lql, lov, lpart, meta, moe_i, moe_f, total;
+    size_t x, f32a, f32b, xn, h, proj, mix, y, xg, u, yrows, us, ys, lqn, lqr, lql, lov, lpart, meta, moe_i, moe_f, rec, f32c, cat, xc, total;
 };
+
+// rows of the input projection and columns of the output projection that ONE mixer owns
+int mixer_rows(const b200_hybrid_layer_t &l) {
+    if (l.mixer == B200_MIXER_ATTN_SCORED) return (l.heads + l.kv_heads) * l.dim + l.kv_heads * l.vdim + (l.out_gate ? l.heads * l.vdim : 0);
+    if (l.mixer == B200_MIXER_DELTA) return 2 * l.kv_heads * l.dim + l.heads * l.vdim + l.heads + l.decay_rank + l.gate_rank;
+    if (l.mixer == B200_MIXER_MLSTM) return 2 * l.heads * l.dim + 2 * l.heads * l.vdim + 2 * l.heads;
+    return 0;
+}
+int cat_cols(const b200_hybrid_layer_t &l) {
+    return l.heads * l.vdim + (l.side ? l.side->heads * l.side->vdim : 0) + (l.mlp == B200_MLP_DENSE ? l.expert_ff : 0);
+}
+int rec_cols(const b200_hybrid_layer_t &l) {
+    if (l.mixer == B200_MIXER_DELTA) return delta_row(l.heads, l.kv_heads, l.dim, l.vdim).ld;
+    if (l.mixer == B200_MIXER_MLSTM) return mlstm_row(l.heads, l.dim, l.vdim).ld;
+    return 0;
+}
 
 int max_rows_of(const b200_hybrid_config_t &c, const b200_hybrid_layer_t &l) {
     const int pairs = c.max_tokens * l.top;
@@ -445,6 +554,7 @@ int max_rows_of(const b200_hybrid_config_t &c, const b200_hybrid_layer_t &l) {
 }
 
 int n_in_of(const b200_hybrid_layer_t &l) {
+    if (l.norm == B200_NORM_LN_PARALLEL) return mixer_rows(l) + (l.side ? mixer_rows(*l.side) : 0) + (l.mlp == B200_MLP_DENSE ? 2 * l.expert_ff : 0);
     if (l.mixer == B200_MIXER_ATTN_CHUNKED) return (2 * l.heads + l.kv_heads) * l.dim;
     if (l.mixer == B200_MIXER_LATENT) return l.heads * (l.dim + l.rot_dim) + l.heads * l.vdim + (l.kv_from < 0 ? l.kv_rank + l.rot_dim : 0);
     return 2 * l.heads * l.dim + 2 * l.heads * l.vdim + l.decay_rank;
@@ -454,6 +564,7 @@ Carve carve(const b200_hybrid *m) {
     const b200_hybrid_config_t &c = m->cfg;
     const size_t T = (size_t)c.max_tokens, es = c.dtype == B200_F32 ? 4 : 2;
     size_t n_in = 1, n_mix = 1, n_f32 = 1, rows = 0, ff = 1, sff = 1, experts = 1, top = 1, lqn = 0, lqr = 0, lql = 0, lov = 0, lheads = 0, lpart = 0;
+    size_t n_rec = 0, n_heads = 0, n_cat = 0;
     const size_t t_pad = (T + 127) / 128 * 128;  // rows per head of the latent mixer's grouped GEMMs
     for (int i = 0; i < c.num_layers; ++i) {
         if (!m->layer_set[i]) continue;
@@ -462,6 +573,16 @@ Carve carve(const b200_hybrid *m) {
         n_mix = std::max(n_mix, (size_t)l.heads * std::max(l.dim, l.vdim));
         n_f32 = std::max(n_f32, (size_t)l.heads * std::max(l.dim, l.vdim));
         n_mix = std::max(n_mix, (size_t)l.heads * l.vdim);
+        if (l.norm == B200_NORM_LN_PARALLEL) {
+            n_cat = std::max(n_cat, (size_t)cat_cols(l));
+            for (const b200_hybrid_layer_t *mx : {&l, l.side}) {
+                if (!mx) continue;
+                n_mix = std::max(n_mix, (size_t)mx->heads * std::max(mx->dim, mx->vdim));
+                n_f32 = std::max(n_f32, (size_t)mx->heads * std::max(mx->dim, mx->vdim));
+                n_rec = std::max(n_rec, (size_t)rec_cols(*mx)), n_heads = std::max(n_heads, (size_t)mx->heads);
+            }
+            continue;
+        }
         if (l.mixer == B200_MIXER_LATENT) {
             lqn = std::max(lqn, (size_t)l.heads * t_pad * l.dim), lqr = std::max(lqr, T * l.heads * l.rot_dim);
             lql = std::max(lql, (size_t)l.heads * t_pad * l.kv_rank), lov = std::max(lov, (size_t)l.heads * t_pad * l.vdim);
@@ -504,8 +625,10 @@ Carve carve(const b200_hybrid *m) {
     k.moe_i = align256((2 * T * top + rows + rows / kMoeTileM + 4) * 4);
     // moe floats: sel_weight [T*top] | row_weight [rows] | shared_gate [T]
     k.moe_f = align256((T * top + rows + T) * 4);
+    k.rec = align256(T * n_rec * 4), k.f32c = align256(2 * T * n_heads * 4), k.cat = align256(T * n_cat * es);
+    k.xc = c.loop_times > 0 ? align256(2 * T * c.width * es) : 0;
     k.total = k.x + k.f32a + k.f32b + k.xn + k.h + k.proj + 2 * k.mix + k.y + k.xg + k.u + k.yrows + k.us + k.ys + k.lqn + k.lqr + 2 * k.lql +
-              k.lov + k.lpart + k.meta + k.moe_i + k.moe_f;
+              k.lov + k.lpart + k.meta + k.moe_i + k.moe_f + k.rec + k.f32c + k.cat + k.xc;
     return k;
 }
 
@@ -527,20 +650,83 @@ b200_hybrid_t *b200_hybrid_create(const b200_hybrid_config_t *cfg) {
     if (!m) return nullptr;
     m->cfg = *cfg;
     m->layers.resize(cfg->num_layers);
+    m->sides.resize(cfg->num_layers);
     m->layer_set.assign(cfg->num_layers, 0);
-    m->plan.resize(cfg->num_layers);
+    if (cfg->loop_times > 0) {
+        if (cfg->loop_start < 0 || cfg->loop_stop <= cfg->loop_start || cfg->loop_stop > cfg->num_layers) {
+            set_error("hybrid_create: looped block [%d, %d) outside the %d layers", cfg->loop_start, cfg->loop_stop, cfg->num_layers);
+            delete m;
+            return nullptr;
+        }
+        for (int i = 0; i < cfg->loop_start; ++i) m->plan.push_back(LayerPlan()), m->plan.back().layer = i;
+        for (int t = 0; t < cfg->loop_times; ++t)
+            for (int i = cfg->loop_start; i < cfg->loop_stop; ++i) {
+                m->plan.push_back(LayerPlan());
+                m->plan.back().layer = i, m->plan.back().entry = i == cfg->loop_start ? t : -1;
+            }
+        for (int i = cfg->loop_stop; i < cfg->num_layers; ++i) m->plan.push_back(LayerPlan()), m->plan.back().layer = i;
+    } else {
+        m->plan.resize(cfg->num_layers);
+        for (int i = 0; i < cfg->num_layers; ++i) m->plan[i].layer = i;
+    }
     return m;
 }
 
 void b200_hybrid_destroy(b200_hybrid_t *m) { delete m; }
 
+static int check_scored_mixer(const b200_hybrid_layer_t *w) {
+    B200_REQUIRE(w->heads > 0 && w->dim > 0 && w->vdim > 0, "hybrid_set_layer: mixer sizes missing");
+    if (w->mixer == B200_MIXER_ATTN_SCORED) {
+        B200_REQUIRE(w->kv_heads > 0 && w->heads % w->kv_heads == 0, "hybrid_set_layer: heads %d not a multiple of kv_heads %d", w->heads, w->kv_heads);
+        B200_REQUIRE(w->rot_dims >= 0 && w->rot_dims <= w->dim && w->rot_dims % 2 == 0 && (w->rot_dims == 0 || w->rot_base > 0.0f),
+                     "hybrid_set_layer: %d rotating dimensions do not fit a head of %d (even, with a positive base)", w->rot_dims, w->dim);
+        B200_REQUIRE(w->window >= 0 && (w->attn_weight == B200_ATTN_SOFTMAX || w->attn_weight == B200_ATTN_SIGMOID), "hybrid_set_layer: bad window or weight kind");
+        B200_REQUIRE((w->dist_r1 == nullptr) == (w->dist_r2 == nullptr), "hybrid_set_layer: the distance penalty needs both of its vectors");
+        B200_REQUIRE((w->q_norm == nullptr) == (w->k_norm == nullptr), "hybrid_set_layer: q and k are normed together or not at all");
+    } else if (w->mixer == B200_MIXER_DELTA) {
+        B200_REQUIRE(w->kv_heads > 0 && w->heads % w->kv_heads == 0, "hybrid_set_layer: heads %d not a multiple of kv_heads %d", w->heads, w->kv_heads);
+        B200_REQUIRE(w->conv >= 1 && w->conv <= 64 && w->conv_w && w->decay_rank > 0 && w->gate_rank > 0 && w->w_decay && w->w_gate2 && w->a_log && w->out_norm,
+                     "hybrid_set_layer: delta-rule sizes / weights missing");
+    } else if (w->mixer == B200_MIXER_MLSTM) {
+        B200_REQUIRE(w->out_norm && w->gate_cap >= 0.0f, "hybrid_set_layer: matrix-memory weights missing");
+    } else {
+        set_error("hybrid_set_layer: mixer kind %d cannot share a norm with the feed-forward", w->mixer);
+        return B200_ERR_INVALID_ARG;
+    }
+    return B200_OK;
+}
+
 int b200_hybrid_set_layer(b200_hybrid_t *m, int layer, const b200_hybrid_layer_t *w) {
     B200_REQUIRE(m && w, "hybrid_set_layer: null argument");
     B200_REQUIRE(layer >= 0 && layer < m->cfg.num_layers, "hybrid_set_layer: layer %d outside [0, %d)", layer, m->cfg.num_layers);
-    B200_REQUIRE(w->mixer == B200_MIXER_ATTN_CHUNKED || w->mixer == B200_MIXER_GLA || w->mixer == B200_MIXER_LATENT,
-                 "hybrid_set_layer: unknown mixer kind %d", w->mixer);
-    B200_REQUIRE(w->norm == B200_NORM_RMS_POST || w->norm == B200_NORM_DYT_PRE_POST, "hybrid_set_layer: unknown norm kind %d", w->norm);
+    B200_REQUIRE(w->mixer >= B200_MIXER_ATTN_CHUNKED && w->mixer <= B200_MIXER_MLSTM, "hybrid_set_layer: unknown mixer kind %d", w->mixer);
+    B200_REQUIRE(w->norm >= B200_NORM_RMS_POST && w->norm <= B200_NORM_LN_PARALLEL, "hybrid_set_layer: unknown norm kind %d", w->norm);
     B200_REQUIRE(w->heads > 0 && w->dim > 0 && w->w_in && w->w_out, "hybrid_set_layer: mixer sizes / weights missing");
+    if (w->norm == B200_NORM_LN_PARALLEL) {
+        // one norm, one input projection, one output projection; the mixers are of the kinds that read a shared projection
+        B200_REQUIRE(w->pre1, "hybrid_set_layer: norm parameters missing");
+        int rc = check_scored_mixer(w);
+        if (rc != B200_OK) return rc;
+        if (w->side) {
+            B200_REQUIRE(!w->side->side, "hybrid_set_layer: a second mixer has no second mixer of its own");
+            if ((rc = check_scored_mixer(w->side)) != B200_OK) return rc;
+        }
+        B200_REQUIRE(w->mlp == B200_MLP_NONE || (w->mlp == B200_MLP_DENSE && w->gated && w->expert_ff > 0),
+                     "hybrid_set_layer: beside a mixer under one norm the feed-forward is a gated dense one or none");
+        B200_REQUIRE(w->act >= B200_ACT_RELU2 && w->act <= B200_ACT_RELU, "hybrid_set_layer: unknown activation %d", w->act);
+        m->layers[layer] = *w;
+        if (w->side) {
+            m->sides[layer] = *w->side;
+            m->layers[layer].side = &m->sides[layer];
+        }
+        m->layer_set[layer] = 1;
+        for (LayerPlan &lp : m->plan)
+            if (lp.layer == layer) lp.n_in = n_in_of(m->layers[layer]);
+        m->scratch = nullptr;
+        return B200_OK;
+    }
+    B200_REQUIRE(w->mixer <= B200_MIXER_LATENT && !w->side, "hybrid_set_layer: mixer kind %d needs the shared-norm layer form", w->mixer);
+    B200_REQUIRE(m->cfg.loop_times == 0, "hybrid_set_layer: only shared-norm layers can be looped");
     if (w->norm == B200_NORM_RMS_POST) B200_REQUIRE(w->norm1, "hybrid_set_layer: norm weight missing");
     else B200_REQUIRE(w->pre1 && w->post1, "hybrid_set_layer: norm parameters missing");
     if (w->mixer == B200_MIXER_ATTN_CHUNKED) {
@@ -561,7 +747,7 @@ int b200_hybrid_set_layer(b200_hybrid_t *m, int layer, const b200_hybrid_layer_t
     if (w->mlp != B200_MLP_NONE) {
         if (w->norm == B200_NORM_RMS_POST) B200_REQUIRE(w->norm2, "hybrid_set_layer: feed-forward norm weight missing");
         else B200_REQUIRE(w->pre2 && w->post2, "hybrid_set_layer: feed-forward norm parameters missing");
-        B200_REQUIRE(w->act >= B200_ACT_RELU2 && w->act <= B200_ACT_GELU_TANH, "hybrid_set_layer: unknown activation %d", w->act);
+        B200_REQUIRE(w->act >= B200_ACT_RELU2 && w->act <= B200_ACT_RELU, "hybrid_set_layer: unknown activation %d", w->act);
         B200_REQUIRE(w->expert_ff > 0 && w->w_up && w->w_down, "hybrid_set_layer: feed-forward sizes / weights missing");
     }
     if (w->mlp == B200_MLP_MOE) {
@@ -578,7 +764,7 @@ int b200_hybrid_set_layer(b200_hybrid_t *m, int layer, const b200_hybrid_layer_t
     }
     m->layers[layer] = *w;
     m->layer_set[layer] = 1;
-    m->plan[layer].n_in = n_in_of(*w);
+    m->plan[layer].n_in = n_in_of(*w);  // (no loop here: run == layer)
     m->scratch = nullptr;  // sizes may have changed
     return B200_OK;
 }
@@ -588,6 +774,15 @@ int b200_hybrid_set_io(b200_hybrid_t *m, const void *embedding, const float *fin
     m->embedding = embedding, m->final_norm = final_norm, m->lm_head = lm_head;
     return B200_OK;
 }
+
+int b200_hybrid_set_loop(b200_hybrid_t *m, const void *w_entry, const float *step) {
+    B200_REQUIRE(m && w_entry && step, "hybrid_set_loop: null argument");
+    B200_REQUIRE(m->cfg.loop_times > 0, "hybrid_set_loop: the engine was created without a looped block");
+    m->w_entry = w_entry, m->loop_step = step;
+    return B200_OK;
+}
+
+int b200_hybrid_num_runs(const b200_hybrid_t *m) { return m ? (int)m->plan.size() : 0; }
 
 size_t b200_hybrid_scratch_bytes(const b200_hybrid_t *m) { return m ? carve(m).total : 0; }
 
@@ -622,29 +817,59 @@ int b200_hybrid_set_scratch(b200_hybrid_t *m, void *ptr, size_t bytes) {
     m->meta = (int *)p, p += k.meta;
     m->moe_i = (int *)p, p += k.moe_i;
     m->moe_f = (float *)p, p += k.moe_f;
+    m->rec = (float *)p, p += k.rec;
+    m->f32c = (float *)p, p += k.f32c;
+    m->cat = p, p += k.cat;
+    m->xc = p, p += k.xc;
     return B200_OK;
 }
+
+namespace {
+// what one mixer of one run takes from the two pools; `plan` (optional) receives the offsets
+void place_mixer(const b200_hybrid_layer_t &l, size_t es, int num_pages, int num_slots, size_t &kv, size_t &stt, MixerPlan *plan) {
+    MixerPlan p;
+    if (l.mixer == B200_MIXER_ATTN_CHUNKED) {
+        const size_t one = align256((size_t)num_pages * l.kv_heads * kPageH * l.dim * es);
+        p.k_off = kv, p.v_off = kv + one, kv += 2 * one;
+    } else if (l.mixer == B200_MIXER_ATTN_SCORED) {
+        p.k_off = kv, kv += align256((size_t)num_pages * l.kv_heads * kPageH * l.dim * es);
+        p.v_off = kv, kv += align256((size_t)num_pages * l.kv_heads * kPageH * l.vdim * es);
+    } else if (l.mixer == B200_MIXER_LATENT) {
+        if (l.kv_from < 0) p.k_off = kv, kv += align256((size_t)num_pages * kPageH * (l.kv_rank + l.rot_dim) * es);
+    } else {
+        p.state_off = stt, stt += align256((size_t)num_slots * l.heads * l.dim * l.vdim * 4);
+        if (l.mixer == B200_MIXER_DELTA) {
+            p.aux_off = stt, stt += align256((size_t)num_slots * std::max(l.conv - 1, 1) * (2 * l.kv_heads * l.dim + l.heads * l.vdim) * 4);
+        } else if (l.mixer == B200_MIXER_MLSTM) {
+            p.aux_off = stt, stt += align256((size_t)num_slots * l.heads * l.dim * 4);
+            p.aux2_off = stt, stt += align256((size_t)num_slots * l.heads * 4);
+        }
+    }
+    if (plan) *plan = p;
+}
+}  // namespace
 
 size_t b200_hybrid_kv_pool_bytes(const b200_hybrid_t *m, int num_pages) {
     if (!m || num_pages <= 0) return 0;
     const size_t es = m->cfg.dtype == B200_F32 ? 4 : 2;
-    size_t total = 0;
-    for (int i = 0; i < m->cfg.num_layers; ++i)
-        if (!m->layer_set[i]) continue;
-        else if (m->layers[i].mixer == B200_MIXER_ATTN_CHUNKED)
-            total += 2 * align256((size_t)num_pages * m->layers[i].kv_heads * kPageH * m->layers[i].dim * es);
-        else if (m->layers[i].mixer == B200_MIXER_LATENT && m->layers[i].kv_from < 0)
-            total += align256((size_t)num_pages * kPageH * (m->layers[i].kv_rank + m->layers[i].rot_dim) * es);
-    return total ? total : 256;
+    size_t kv = 0, stt = 0;
+    for (const LayerPlan &lp : m->plan) {
+        if (!m->layer_set[lp.layer]) continue;
+        place_mixer(m->layers[lp.layer], es, num_pages, 1, kv, stt, nullptr);
+        if (m->layers[lp.layer].side) place_mixer(*m->layers[lp.layer].side, es, num_pages, 1, kv, stt, nullptr);
+    }
+    return kv ? kv : 256;
 }
 
 size_t b200_hybrid_state_pool_bytes(const b200_hybrid_t *m, int num_slots) {
     if (!m || num_slots <= 0) return 0;
-    size_t total = 0;
-    for (int i = 0; i < m->cfg.num_layers; ++i)
-        if (m->layer_set[i] && m->layers[i].mixer == B200_MIXER_GLA)
-            total += align256((size_t)num_slots * m->layers[i].heads * m->layers[i].dim * m->layers[i].vdim * 4);
-    return total ? total : 256;
+    size_t kv = 0, stt = 0;
+    for (const LayerPlan &lp : m->plan) {
+        if (!m->layer_set[lp.layer]) continue;
+        place_mixer(m->layers[lp.layer], 2, 1, num_slots, kv, stt, nullptr);
+        if (m->layers[lp.layer].side) place_mixer(*m->layers[lp.layer].side, 2, 1, num_slots, kv, stt, nullptr);
+    }
+    return stt ? stt : 256;
 }
 
 int b200_hybrid_set_pools(b200_hybrid_t *m, void *kv_pool, int num_pages, void *state_pool, int num_slots) {
@@ -652,24 +877,19 @@ int b200_hybrid_set_pools(b200_hybrid_t *m, void *kv_pool, int num_pages, void *
     B200_REQUIRE(((uintptr_t)kv_pool & 255) == 0 && ((uintptr_t)state_pool & 255) == 0, "hybrid_set_pools: pools must be 256-byte aligned");
     const size_t es = m->cfg.dtype == B200_F32 ? 4 : 2;
     size_t kv = 0, stt = 0;
-    for (int i = 0; i < m->cfg.num_layers; ++i) {
+    for (size_t r = 0; r < m->plan.size(); ++r) {
+        LayerPlan &lp = m->plan[r];
+        const int i = lp.layer;
         B200_REQUIRE(m->layer_set[i], "hybrid_set_pools: layer %d not set", i);
         const b200_hybrid_layer_t &l = m->layers[i];
-        if (l.mixer == B200_MIXER_ATTN_CHUNKED) {
-            const size_t one = align256((size_t)num_pages * l.kv_heads * kPageH * l.dim * es);
-            m->plan[i].k_off = kv, m->plan[i].v_off = kv + one, kv += 2 * one;
-        } else if (l.mixer == B200_MIXER_LATENT) {
-            if (l.kv_from < 0) {
-                m->plan[i].k_off = kv, kv += align256((size_t)num_pages * kPageH * (l.kv_rank + l.rot_dim) * es);
-            } else {  // the rows of an earlier layer, which must own them and rotate them alike
-                const b200_hybrid_layer_t &o = m->layers[l.kv_from];
-                B200_REQUIRE(o.mixer == B200_MIXER_LATENT && o.kv_from < 0 && o.kv_rank == l.kv_rank && o.rot_dim == l.rot_dim &&
-                                 o.rot_dims == l.rot_dims && o.rot_base == l.rot_base,
-                             "hybrid_set_pools: layer %d cannot read the latent rows of layer %d (no cache of its own, or other sizes)", i, l.kv_from);
-                m->plan[i].k_off = m->plan[l.kv_from].k_off;
-            }
-        } else {
-            m->plan[i].state_off = stt, stt += align256((size_t)num_slots * l.heads * l.dim * l.vdim * 4);
+        place_mixer(l, es, num_pages, num_slots, kv, stt, &lp);
+        if (l.side) place_mixer(*l.side, es, num_pages, num_slots, kv, stt, &lp.side);
+        if (l.mixer == B200_MIXER_LATENT && l.kv_from >= 0) {  // the rows of an earlier layer, which must own them and rotate them alike
+            const b200_hybrid_layer_t &o = m->layers[l.kv_from];
+            B200_REQUIRE(o.mixer == B200_MIXER_LATENT && o.kv_from < 0 && o.kv_rank == l.kv_rank && o.rot_dim == l.rot_dim &&
+                             o.rot_dims == l.rot_dims && o.rot_base == l.rot_base,
+                         "hybrid_set_pools: layer %d cannot read the latent rows of layer %d (no cache of its own, or other sizes)", i, l.kv_from);
+            lp.k_off = m->plan[l.kv_from].k_off;  // (latent layers are never looped: run == layer)
         }
     }
     m->kv_pool = (char *)kv_pool, m->state_pool = (char *)state_pool, m->num_pages = num_pages, m->num_slots = num_slots;
@@ -777,8 +997,112 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
         if (rc != B200_OK) return rc; \
     } while (0)
     // 16-bit engines: every kernel that writes the residual stream also writes its 16-bit copy h, which the next projections read
+    const int n_runs = (int)m->plan.size();
+    const bool shared_norm = m->layers[0].norm == B200_NORM_LN_PARALLEL;  // layers of one norm whose sublayers share the projections
+    for (int i = 0; i < c.num_layers; ++i)
+        B200_REQUIRE((m->layers[i].norm == B200_NORM_LN_PARALLEL) == shared_norm, "hybrid_forward: shared-norm layers and others do not mix in one model");
+    if (c.loop_times > 0 && (!m->w_entry || !m->loop_step)) {
+        set_error("hybrid_forward: the looped block's entry weights are not set");
+        return B200_ERR_STATE;
+    }
+    const size_t es = f32 ? 4 : 2;
+    // the residual step of a shared-norm layer; it also writes what the next run reads: its normed input, or (before an entry step) x itself
+    auto ln_residual = [&](const void *y, const float *y32, const float *bias, const float *ln, void *h_out, int h_ld, float *trace) -> int {
+        B200_DISPATCH_DTYPE(dt, {
+            ln_residual_kernel<T><<<NT, 256, (size_t)width * sizeof(float), st>>>(m->x, (const T *)y, y32, bias, y32 ? 1 : 0, ln, c.norm_eps, width,
+                                                                                (T *)h_out, h_ld, trace);
+        });
+        return cuda_status("ln_residual launch");
+    };
+    // hands x over to run `run`: the normed input of its layer, or x itself into the left half of the entry step's input row
+    auto hand_over = [&](int run, const void *y, const float *bias, float *trace) -> int {
+        if (run >= n_runs) return (y || bias || trace) ? ln_residual(y, nullptr, bias, nullptr, nullptr, 0, trace) : B200_OK;
+        if (m->plan[run].entry >= 0) return ln_residual(y, nullptr, bias, nullptr, m->xc, 2 * width, trace);
+        return ln_residual(y, nullptr, bias, m->layers[m->plan[run].layer].pre1, m->h, width, trace);
+    };
+    if (shared_norm) {
+        B200_DISPATCH_DTYPE(dt, {
+            embed_rows_kernel<T><<<NT, 128, 0, st>>>(d_ids, (const T *)m->embedding, m->x, c.loop_times > 0 ? (T *)m->xc + width : nullptr, 2 * width, width,
+                                                    c.vocab, c.embed_scale != 0.0f ? c.embed_scale : 1.0f);
+        });
+        RUN(hand_over(0, nullptr, nullptr, nullptr));
+    } else {
     B200_DISPATCH_DTYPE(dt, { embed_f32_kernel<T><<<NT, 128, 0, st>>>(d_ids, (const T *)m->embedding, m->x, f32 ? nullptr : (T *)m->h, width, c.vocab,
                                                                       c.embed_scale != 0.0f ? c.embed_scale : 1.0f); });
+    }
+
+    // one mixer of a shared-norm layer: reads its rows of the projection from column `col`, writes its heads at column `ocol` of the
+    // output projection's input row, scaled
+    auto run_mixer = [&](const b200_hybrid_layer_t &l, const MixerPlan &mp, int n_in, int col, int n_cat, int ocol, float out_scale) -> int {
+        char *out = (char *)m->cat + (size_t)ocol * es;
+        if (l.mixer == B200_MIXER_ATTN_SCORED) {
+            const char *gate = l.out_gate ? (const char *)m->proj + (size_t)(col + (l.heads + l.kv_heads) * l.dim + l.kv_heads * l.vdim) * es : nullptr;
+            char *kp = m->kv_pool + mp.k_off, *vp = m->kv_pool + mp.v_off;
+            const int sig = l.attn_weight == B200_ATTN_SIGMOID;
+            RUN(launch_scored_prep(dt, m->proj, n_in, col, l.b_in, m->mix, kp, vp, l.q_norm, l.k_norm, c.norm_eps, d_seq, d_pos, d_bt, mpps, NT, l.heads,
+                                   l.kv_heads, l.dim, l.vdim, l.rot_dims, l.rot_base, st));
+            const int max_keys = l.window > 0 ? std::min(l.window, mpps * kPageH) : mpps * kPageH;
+            if (scored_attention_tiles_supported(dt, l.dim, l.vdim, n_in, n_cat, l.window, l.dist_r1 != nullptr)) {
+                RUN(launch_scored_attention_tiles(dt, m->mix, kp, vp, l.head_bias, l.dist_r1, l.dist_r2, gate, n_in, out, n_cat, out_scale, d_tiles, n_tiles,
+                                                  d_bt, mpps, l.heads, l.kv_heads, l.dim, l.vdim, l.scale, l.window, sig, st));
+                RUN(launch_scored_attention(dt, m->mix, kp, vp, l.head_bias, l.dist_r1, l.dist_r2, gate, n_in, out, n_cat, out_scale, d_seq, d_pos, d_bt,
+                                            mpps, n_short, l.heads, l.kv_heads, l.dim, l.vdim, l.scale, l.window, sig, max_keys, st, d_short));
+            } else {
+                RUN(launch_scored_attention(dt, m->mix, kp, vp, l.head_bias, l.dist_r1, l.dist_r2, gate, n_in, out, n_cat, out_scale, d_seq, d_pos, d_bt,
+                                            mpps, NT, l.heads, l.kv_heads, l.dim, l.vdim, l.scale, l.window, sig, max_keys, st));
+            }
+        } else if (l.mixer == B200_MIXER_DELTA) {
+            float *conv_state = (float *)(m->state_pool + mp.aux_off);
+            const DeltaRow lay = delta_row(l.heads, l.kv_heads, l.dim, l.vdim);
+            RUN(launch_delta_prep(dt, m->proj, n_in, col, l.conv_w, l.conv, conv_state, l.w_decay, l.decay_bias, l.a_log, l.decay_rank, l.w_gate2,
+                                  l.gate_rank, m->rec, d_seq, d_pos, d_start, d_pos0, d_slot, NT, l.heads, l.kv_heads, l.dim, l.vdim, st));
+            RUN(launch_conv_state_update(dt, m->proj, n_in, col, conv_state, l.conv, 2 * l.kv_heads * l.dim + l.heads * l.vdim, d_start, d_pos0, d_slot, S, st));
+            RUN(launch_delta_recurrent(m->rec, (float *)(m->state_pool + mp.state_off), m->f32b, d_start, d_pos0, d_slot, S, l.heads, l.kv_heads, l.dim,
+                                       l.vdim, st));
+            RUN(launch_head_output(dt, m->f32b, nullptr, nullptr, l.out_norm, 0, c.norm_eps, m->rec + lay.gate, lay.ld, nullptr, 0, out, n_cat, out_scale, NT,
+                                   l.heads, l.vdim, st));
+        } else {
+            const char *gate = (const char *)m->proj + (size_t)(col + 2 * l.heads * l.dim + l.heads * l.vdim) * es;
+            float *nq = m->f32c, *mo = m->f32c + (size_t)NT * l.heads;
+            RUN(launch_mlstm_prep(dt, m->proj, n_in, col, l.b_in, l.gate_cap, m->rec, NT, l.heads, l.dim, l.vdim, st));
+            RUN(launch_mlstm_recurrent(m->rec, (float *)(m->state_pool + mp.state_off), (float *)(m->state_pool + mp.aux_off),
+                                       (float *)(m->state_pool + mp.aux2_off), m->f32b, nq, mo, d_start, d_pos0, d_slot, S, l.heads, l.dim, l.vdim, st));
+            RUN(launch_head_output(dt, m->f32b, nq, mo, l.out_norm, l.vdim, c.norm_eps, nullptr, 0, gate, n_in, out, n_cat, out_scale, NT, l.heads, l.vdim, st));
+        }
+        return B200_OK;
+    };
+    // a shared-norm layer run: (entry step) -> one input projection -> mixers and the gated inner row side by side -> one output
+    // projection -> residual + the next run's normed input
+    auto shared_norm_layer = [&](int run) -> int {
+        const LayerPlan &lp = m->plan[run];
+        const b200_hybrid_layer_t &l = m->layers[lp.layer];
+        if (lp.entry >= 0) {  // x <- w_entry [x ; x0] + step[pass], fp32 out; then this layer's norm
+            rc = launch_dense_f32out(dt, m->xc, m->w_entry, m->xn, NT, width, 2 * width, st);
+            if (rc == B200_ERR_UNSUPPORTED) rc = launch_proj_f32(dt, m->xc, 2 * width, dt, m->w_entry, nullptr, m->xn, width, NT, width, 2 * width, st);
+            if (rc != B200_OK) return rc;
+            RUN(ln_residual(nullptr, m->xn, m->loop_step + (size_t)lp.entry * width, l.pre1, m->h, width, nullptr));
+        }
+        const int n_cat = cat_cols(l);
+        RUN(linear(m, m->h, l.w_in, m->proj, NT, width, lp.n_in, st));
+        int col = 0, ocol = 0;
+        RUN(run_mixer(l, lp, lp.n_in, col, n_cat, ocol, l.side && l.mix_scale != 0.0f ? l.mix_scale : 1.0f));
+        col += mixer_rows(l), ocol += l.heads * l.vdim;
+        if (l.side) {
+            RUN(run_mixer(*l.side, lp.side, lp.n_in, col, n_cat, ocol, l.side_scale != 0.0f ? l.side_scale : 1.0f));
+            col += mixer_rows(*l.side), ocol += l.side->heads * l.side->vdim;
+        }
+        if (l.mlp == B200_MLP_DENSE) {
+            const size_t n = (size_t)NT * l.expert_ff;
+            B200_DISPATCH_DTYPE(dt, {
+                gated_act_strided_kernel<T><<<(unsigned)std::min<size_t>((n + 255) / 256, 148 * 16), 256, 0, st>>>(
+                    (const T *)m->proj, lp.n_in, col, col + l.expert_ff, (T *)m->cat + ocol, n_cat, NT, l.expert_ff, l.act);
+            });
+            RUN(cuda_status("gated_act_strided launch"));
+        }
+        RUN(linear(m, m->cat, l.w_out, m->y, NT, n_cat, width, st));
+        return hand_over(run + 1, m->y, l.b_out, layer_trace ? layer_trace + (size_t)run * NT * width : nullptr);
+    };
+
     auto cast_x = [&]() -> const void * { return f32 ? (const void *)m->x : (const void *)m->h; };
     auto postnorm = [&](const void *y_dense, const void *y_rows, const int *pair_row, int top, const void *y_shared, const float *gate,
                         const float *g, float *trace) -> int {
@@ -811,10 +1135,13 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
         if (li + 1 >= c.num_layers) return nullptr;
         return m->layers[li + 1].norm == B200_NORM_DYT_PRE_POST ? m->layers[li + 1].pre1 : nullptr;
     };
-    const size_t es = f32 ? 4 : 2;
     bool h_normed = false;  // m->h holds the pre-normed input of the coming sublayer
 
-    for (int li = 0; li < c.num_layers; ++li) {
+    for (int li = 0; li < n_runs; ++li) {  // (only shared-norm layers loop: elsewhere a run is its layer)
+        if (shared_norm) {
+            RUN(shared_norm_layer(li));
+            continue;
+        }
         const b200_hybrid_layer_t &l = m->layers[li];
         const LayerPlan &lp = m->plan[li];
         const bool dyt = l.norm == B200_NORM_DYT_PRE_POST;
@@ -972,7 +1299,8 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
     if (W > 0) {
         // the wanted rows only: final norm (fp32 and, for 16-bit engines, a 16-bit copy in h), then the LM head with fp32 logits
         B200_DISPATCH_DTYPE(dt, {
-            if (c.final_norm == B200_NORM_DYT_PRE_POST) final_dyt_rows_kernel<T><<<W, 256, 0, st>>>(m->x, d_want, m->final_norm, m->xn, f32 ? nullptr : (T *)m->h, width);
+            if (c.final_norm == B200_NORM_LN_PARALLEL) final_ln_rows_kernel<T><<<W, 256, 0, st>>>(m->x, d_want, m->final_norm, c.norm_eps, m->xn, f32 ? nullptr : (T *)m->h, width);
+            else if (c.final_norm == B200_NORM_DYT_PRE_POST) final_dyt_rows_kernel<T><<<W, 256, 0, st>>>(m->x, d_want, m->final_norm, m->xn, f32 ? nullptr : (T *)m->h, width);
             else final_norm_rows_kernel<T><<<W, 256, 0, st>>>(m->x, d_want, m->final_norm, c.norm_eps, m->xn, f32 ? nullptr : (T *)m->h, width);
         });
         rc = launch_dense_f32out(dt, m->h, m->lm_head, logits, W, c.vocab, width, st);

@@ -34,6 +34,43 @@ int launch_latent_attention_tiles(int dtype, const void *ql, const void *qr, con
 int launch_latent_gate(int dtype, const void *ov, const void *gate_in, int gate_ld, void *out, int tokens, int t_pad, int heads, int vdim,
                        cudaStream_t st);
 
+// attention_scored.cu: proj [tokens, ld] holds q (heads*dim), k (kv_heads*dim), v (kv_heads*vdim) from column col0 on; b_in (optional) is
+// counted from the same row.  q_out [tokens, heads*dim]; pools K [pages, kv_heads, page, dim], V [pages, kv_heads, page, vdim]
+int launch_scored_prep(int dtype, const void *proj, int ld, int col0, const float *b_in, void *q_out, void *k_pool, void *v_pool,
+                       const float *q_norm, const float *k_norm, float eps, const int *tok_seq, const int *tok_pos, const int *block_table,
+                       int mpps, int tokens, int heads, int kv_heads, int dim, int vdim, int rot_dims, float rot_base, cudaStream_t st);
+int launch_scored_attention(int dtype, const void *q, const void *k_pool, const void *v_pool, const float *head_bias, const float *dist_r1,
+                            const float *dist_r2, const void *gate_in, int gate_ld, void *out, int out_ld, float out_scale, const int *tok_seq,
+                            const int *tok_pos, const int *block_table, int mpps, int tokens, int heads, int kv_heads, int dim, int vdim,
+                            float scale, int window, int sigmoid, int max_keys, cudaStream_t st, const int *tok_list = nullptr);
+bool scored_attention_tiles_supported(int dtype, int dim, int vdim, int gate_ld, int out_ld, int window, bool penalty);
+int launch_scored_attention_tiles(int dtype, const void *q, const void *k_pool, const void *v_pool, const float *head_bias, const float *dist_r1,
+                                  const float *dist_r2, const void *gate_in, int gate_ld, void *out, int out_ld, float out_scale,
+                                  const int *tiles, int n_tiles, const int *block_table, int mpps, int heads, int kv_heads, int dim, int vdim,
+                                  float scale, int window, int sigmoid, cudaStream_t st);
+
+// recurrent.cu: column offsets of the fp32 row per token that the prep kernels write and the recurrences read
+struct DeltaRow { int q, k, v, decay, gate, beta, ld; };
+struct MlstmRow { int q, k, v, gi, gf, ld; };
+DeltaRow delta_row(int heads, int kv_heads, int dim, int vdim);
+MlstmRow mlstm_row(int heads, int dim, int vdim);
+int launch_delta_prep(int dtype, const void *proj, int ld, int col0, const float *conv_w, int taps, float *conv_state, const void *w_decay,
+                      const float *decay_bias, const float *a_log, int rank, const void *w_gate2, int gate_rank, float *rec, const int *tok_seq,
+                      const int *tok_pos, const int *seq_start, const int *seq_pos0, const int *seq_slot, int tokens, int heads, int kv_heads,
+                      int dim, int vdim, cudaStream_t st);
+int launch_conv_state_update(int dtype, const void *proj, int ld, int col0, float *conv_state, int taps, int channels, const int *seq_start,
+                             const int *seq_pos0, const int *seq_slot, int n_seqs, cudaStream_t st);
+int launch_delta_recurrent(const float *rec, float *S, float *o, const int *seq_start, const int *seq_pos0, const int *seq_slot, int n_seqs,
+                           int heads, int kv_heads, int dim, int vdim, cudaStream_t st);
+int launch_mlstm_prep(int dtype, const void *proj, int ld, int col0, const float *b_in, float cap, float *rec, int tokens, int heads, int dim,
+                      int vdim, cudaStream_t st);
+int launch_mlstm_recurrent(const float *rec, float *S, float *n_state, float *m_state, float *o, float *nq, float *m_out, const int *seq_start,
+                           const int *seq_pos0, const int *seq_slot, int n_seqs, int heads, int dim, int vdim, cudaStream_t st);
+// out[t, h*vdim + j] = out_scale * y * rsqrt(mean_j y^2 + eps) * w[h*w_stride + j] * sigmoid(gate); y = o, or o / (max(|nq|, exp(-m)) + 1e-6)
+int launch_head_output(int dtype, const float *o, const float *nq, const float *m_in, const float *w, int w_stride, float eps,
+                       const float *gate_f, int gate_f_ld, const void *gate_t, int gate_t_ld, void *out, int out_ld, float out_scale, int tokens,
+                       int heads, int vdim, cudaStream_t st);
+
 // gla.cu
 // decay[t, c] = sigmoid(z)^(1/tau), z = w_decay[c, :] . proj[t, col0 : col0 + rank] + bias[c]   (fp32 from the projection on)
 int launch_gla_decay(int dtype, const void *proj, int ld, int col0, const void *w_decay, const float *bias, float tau, float *decay,
