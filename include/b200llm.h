@@ -538,7 +538,7 @@ typedef struct b200_hybrid_layer_s {
     float gate_cap;               /* log gates: i = cap * tanh(z_i / cap), f = logsigmoid(cap * tanh(z_f / cap))                      */
     /* ---- a second mixer beside the first: both read the same input, result = mix_scale * mixer + side_scale * side mixer */
     const struct b200_hybrid_layer_s *side; /* only its mixer fields are read (LN_PARALLEL layers); NULL: none                        */
-    float mix_scale, side_scale;  /* 0 reads as 1                                                                                     */
+    float mix_scale, side_scale;  /* read only when there is a second mixer                                                           */
 } b200_hybrid_layer_t;
 
 typedef struct {

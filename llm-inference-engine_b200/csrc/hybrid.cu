@@ -1085,10 +1085,10 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
         const int n_cat = cat_cols(l);
         RUN(linear(m, m->h, l.w_in, m->proj, NT, width, lp.n_in, st));
         int col = 0, ocol = 0;
-        RUN(run_mixer(l, lp, lp.n_in, col, n_cat, ocol, l.side && l.mix_scale != 0.0f ? l.mix_scale : 1.0f));
+        RUN(run_mixer(l, lp, lp.n_in, col, n_cat, ocol, l.side ? l.mix_scale : 1.0f));
         col += mixer_rows(l), ocol += l.heads * l.vdim;
         if (l.side) {
-            RUN(run_mixer(*l.side, lp.side, lp.n_in, col, n_cat, ocol, l.side_scale != 0.0f ? l.side_scale : 1.0f));
+            RUN(run_mixer(*l.side, lp.side, lp.n_in, col, n_cat, ocol, l.side_scale));
             col += mixer_rows(*l.side), ocol += l.side->heads * l.side->vdim;
         }
         if (l.mlp == B200_MLP_DENSE) {

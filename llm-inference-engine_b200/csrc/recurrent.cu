@@ -45,10 +45,10 @@ __global__ void __launch_bounds__(256)
 delta_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__restrict__ conv_w, int taps, const float *__restrict__ conv_state,
                   const T *__restrict__ w_decay, const float *__restrict__ decay_bias, const float *__restrict__ a_log, int rank,
                   const T *__restrict__ w_gate2, int gate_rank, float *__restrict__ rec, DeltaRow lay, const int *__restrict__ tok_seq,
-                  const int *__restrict__ tok_pos, const int *__restrict__ seq_start, const int *__restrict__ seq_pos0,
-                  const int *__restrict__ seq_slot, int heads, int kv_heads, int dim, int vdim) {
+                  const int *__restrict__ tok_pos, const int *__restrict__ seq_pos0, const int *__restrict__ seq_slot, int heads, int kv_heads, int dim,
+                  int vdim) {
     extern __shared__ float sh[];  // conv outputs [channels] | decay-in [rank] | gate-in [gate_rank]
-    const int t = blockIdx.x, s = tok_seq[t], pos = tok_pos[t], t0 = seq_start[s], pos0 = seq_pos0[s], slot = seq_slot[s];
+    const int t = blockIdx.x, s = tok_seq[t], pos = tok_pos[t], pos0 = seq_pos0[s], slot = seq_slot[s];
     const int nqk = kv_heads * dim, nv = heads * vdim, channels = 2 * nqk + nv;
     float *cv = sh, *zin = cv + channels, *gin = zin + rank;
     const float *cst = conv_state + (size_t)slot * (taps - 1) * channels;
@@ -327,8 +327,8 @@ int launch_delta_prep(int dtype, const void *proj, int ld, int col0, const float
     B200_DISPATCH_DTYPE(dtype, {
         if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         delta_prep_kernel<T><<<tokens, 256, smem, st>>>((const T *)proj, ld, col0, conv_w, taps, conv_state, (const T *)w_decay, decay_bias, a_log, rank,
-                                                       (const T *)w_gate2, gate_rank, rec, lay, tok_seq, tok_pos, seq_start, seq_pos0, seq_slot, heads,
-                                                       kv_heads, dim, vdim);
+                                                       (const T *)w_gate2, gate_rank, rec, lay, tok_seq, tok_pos, seq_pos0, seq_slot, heads, kv_heads, dim,
+                                                       vdim);
     });
     return cuda_status("delta_prep launch");
 }

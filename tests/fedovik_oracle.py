@@ -196,3 +196,107 @@ def forward(config, tensors, tokens, trace=False):
         seen.append(x.clone())
     logits = layer_norm(x, d(tensors["final.norm"]), d(tensors["final.norm.b"]), eps) @ emb.T
     return (logits, torch.stack(seen)) if trace else logits
+
+
+# ------------------------------------------------------------------ small random models for the tests
+def attention_layer(heads=4, kv_heads=2, dim=16, vdim=8, rot_dims=None, base=10000.0, scale=None, mlp=None):
+    rot_dims = dim if rot_dims is None else rot_dims
+    mx = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=dim ** -0.5 if scale is None else scale)
+    if rot_dims:
+        mx["rot"] = dict(base=base, dims=rot_dims)
+    return dict(type="attention", mixer=mx, mlp=mlp)
+
+
+def pair_layer(heads=4, kv_heads=2, dim=16, vdim=24, window=24, scale=None, left_scale=0.7, right_scale=1.1, r_heads=2, r_kv_heads=1, r_dim=8,
+               r_vdim=16, conv=4, mlp=None):
+    left = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=dim ** -0.5 if scale is None else scale, mask=dict(size=window))
+    right = dict(heads=r_heads, kv_heads=r_kv_heads, dim=r_dim, vdim=r_vdim, conv=conv)
+    return dict(type="parallel", mixer=dict(left=left, right=right, left_scale=left_scale, right_scale=right_scale), mlp=mlp)
+
+
+def mlstm_layer(heads=2, dim=12, vdim=16, gate_cap=8.0, mlp=None):
+    return dict(type="mlstm", mixer=dict(heads=heads, dim=dim, vdim=vdim, gate_cap=gate_cap), mlp=mlp)
+
+
+def dense(ff=40):
+    return dict(kind="dense", ff=ff)
+
+
+def make_config(layers, width=32, vocab=50, embed_scale=2.0, loop=None, eps=1e-5):
+    config = dict(architecture="Fedovik", width=width, vocab=vocab, embedding=dict(scale=embed_scale), norm=dict(eps=eps), layers=layers)
+    if loop:
+        config["loop"] = dict(start=loop[0], stop=loop[1], times=loop[2])
+    return config
+
+
+def make_weights(config, seed=0, low_rank=6):
+    """Random weights whose values are exact in bfloat16: (float64 dict for this file, bfloat16 dict as a checkpoint holds them)."""
+    gen = torch.Generator().manual_seed(seed)
+    w = config["width"]
+    P = {}
+
+    def lin(name, out, inp, gain=1.0):
+        P[name] = torch.randn(out, inp, generator=gen) * gain / math.sqrt(inp)
+
+    def vec(name, n, mean=0.0, std=0.1):
+        P[name] = mean + std * torch.randn(n, generator=gen)
+
+    P["embed"] = torch.randn(config["vocab"], w, generator=gen)
+    if config.get("loop"):
+        P["loop.in"] = torch.cat([torch.eye(w), 0.3 * torch.eye(w)], 1) + 0.3 * torch.randn(w, 2 * w, generator=gen) / math.sqrt(w)
+        vec("loop.step", config["loop"]["times"] * w)
+        P["loop.step"] = P["loop.step"].view(config["loop"]["times"], w)
+    for i, L in enumerate(config["layers"]):
+        p, mx = f"l{i}.", L["mixer"]
+        vec(p + "norm1", w, 1.0), vec(p + "norm1.b", w)
+
+        def attention(pre, a, sigmoid):
+            H, G, dk, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            lin(pre + "q", H * dk, w, 2.0), lin(pre + "k", G * dk, w, 2.0), lin(pre + "v", G * dv, w), lin(pre + "o", w, H * dv)
+            vec(pre + "q.b", H * dk, 0.0, 0.3), vec(pre + "k.b", G * dk, 0.0, 0.3), vec(pre + "v.b", G * dv)
+            if sigmoid:
+                lin(pre + "g", H * dv, w), vec(pre + "o.b", w), vec(pre + "pb", H, -2.0, 0.5)
+            else:
+                vec(pre + "q.norm", dk, 1.0, 0.2), vec(pre + "k.norm", dk, 1.0, 0.2)
+                P[pre + "r1"] = 0.2 + torch.rand(H, generator=gen)
+                P[pre + "r2"] = 0.5 + torch.rand(H, generator=gen)
+
+        if L["type"] == "attention":
+            attention(p + "mix.", mx, True)
+        elif L["type"] == "parallel":
+            attention(p + "mix.left.", mx["left"], False)
+            r, pre = mx["right"], p + "mix.right."
+            H, G, dk, dv = r["heads"], r["kv_heads"], r["dim"], r["vdim"]
+            lin(pre + "q", G * dk, w), lin(pre + "k", G * dk, w), lin(pre + "v", H * dv, w), lin(pre + "b", H, w), lin(pre + "o", w, H * dv)
+            for n, c in (("q", G * dk), ("k", G * dk), ("v", H * dv)):
+                P[pre + n + ".conv"] = 0.6 * torch.randn(c, r["conv"], generator=gen)
+            lin(pre + "a1", low_rank, w), lin(pre + "a2", H * dk, low_rank, 2.0), vec(pre + "dt_bias", H * dk, -1.0, 1.0)
+            P[pre + "A_log"] = -1.5 + 2.0 * torch.rand(H, generator=gen)
+            lin(pre + "g1", low_rank + 1, w), lin(pre + "g2", H * dv, low_rank + 1, 2.0), vec(pre + "norm", dv, 1.0, 0.2)
+        else:
+            H, dk, dv = mx["heads"], mx["dim"], mx["vdim"]
+            pre = p + "mix."
+            lin(pre + "q", H * dk, w), lin(pre + "k", H * dk, w), lin(pre + "v", H * dv, w), lin(pre + "g", H * dv, w), lin(pre + "o", w, H * dv)
+            lin(pre + "i", H, w, 3.0), lin(pre + "f", H, w, 3.0), vec(pre + "i.b", H, 0.0, 1.0), vec(pre + "f.b", H, 2.0, 1.0)
+            vec(pre + "norm", H * dv, 1.0, 0.2)
+        if L.get("mlp"):
+            ff = L["mlp"]["ff"]
+            lin(p + "mlp.gate", ff, w), lin(p + "mlp.up", ff, w), lin(p + "mlp.down", w, ff)
+    vec("final.norm", w, 1.0), vec("final.norm.b", w)
+    packed = {k: v.to(torch.bfloat16) for k, v in P.items()}
+    return {k: v.double() for k, v in packed.items()}, packed
+
+
+def rel_err(got, want):
+    got, want = torch.as_tensor(got, dtype=F64), torch.as_tensor(want, dtype=F64)
+    return float((got - want).norm() / want.norm().clamp(min=1e-30))
+
+
+def greedy(config, W, prompt, n_new):
+    """Greedy continuation (ties: the lower id), the whole sequence read anew for every token."""
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(torch.argmax(forward(config, W, toks)[-1]))
+        toks.append(nxt)
+        out.append(nxt)
+    return out
