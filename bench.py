@@ -719,6 +719,10 @@ def workload_config(args, cfg):
 
 
 def run_hybrid(args):
+    print(json.dumps(hybrid_result(args)), flush=True)
+
+
+def hybrid_result(args):
     """--mode hybrid: prefill and decode throughput of a Vasolix-shaped model (random weights, bf16) on the layer-list decoder, at one of
     HYBRID_SIZES.  Prefill: one prompt of --prefill-tokens tokens in one engine call.  Decode: --batch sequences with --ctx cached positions
     each, one token per sequence per step, through the same call a served request takes (host batch description in, device logits out).
@@ -819,7 +823,7 @@ def run_hybrid(args):
     kv_bytes = 2 * es * 2 * B * A["kv_heads"] * A["dim"] * (ctx % chunk + 1) * 1.0
     st_bytes = 2 * 4 * 2 * B * G["heads"] * G["dim"] * G["vdim"]
     dec_gbs = (w_bytes + kv_bytes + st_bytes) / (dec_ms * 1e-3) / 1e9
-    print(json.dumps({
+    return ({
         "metric": "hybrid prefill / decode tokens/s", "value": Tq * 1e3 / pre_ms, "unit": "tokens/s (prefill)", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "b200",
         "config": {"model": f"Vasolix-shaped, size {args.hybrid_size}: width {W}, 4 layers (gla, attention, gla, attention), {M['experts']} experts top {M['top']}",
@@ -828,6 +832,149 @@ def run_hybrid(args):
                     "frac_of_measured_bf16_sustained": pre_tflops / float(peaks.get("bf16_tflops_sustained", 1400.0)), "clocks": pre_clocks},
         "decode": {"tokens_per_s": B * 1e3 / dec_ms, "ms_per_step": dec_ms, "algorithmic_gb_per_s": dec_gbs,
                    "frac_of_measured_hbm": dec_gbs / float(peaks.get("hbm_gbs", 6650.0)), "clocks": dec_clocks},
+        "e2e": "both numbers are taken through HybridDecoder.forward: host batch description in (one H2D copy per call), device logits out"})
+
+
+SHARED_NORM_SIZES = {  # Fedovik-shaped layer lists (attention, parallel, mlstm, parallel; the first two layers run twice), random weights
+    "s": dict(width=1024, ff=2816, attn=dict(heads=8, kv_heads=2, dim=128, vdim=64), left=dict(heads=8, kv_heads=2, dim=128, vdim=128, window=512),
+              right=dict(heads=4, kv_heads=4, dim=64, vdim=256, rank=32), mlstm=dict(heads=4, dim=128, vdim=256)),
+    "m": dict(width=2048, ff=5632, attn=dict(heads=16, kv_heads=4, dim=128, vdim=64), left=dict(heads=16, kv_heads=4, dim=128, vdim=128, window=1024),
+              right=dict(heads=8, kv_heads=8, dim=128, vdim=256, rank=64), mlstm=dict(heads=8, dim=128, vdim=256)),
+    "l": dict(width=4096, ff=11008, attn=dict(heads=32, kv_heads=8, dim=128, vdim=64), left=dict(heads=32, kv_heads=8, dim=128, vdim=128, window=2048),
+              right=dict(heads=16, kv_heads=16, dim=128, vdim=256, rank=64), mlstm=dict(heads=16, dim=128, vdim=256)),
+}
+
+
+def run_fedovik(args):
+    """--mode fedovik: prefill and decode throughput of a Fedovik-shaped model (random weights, bf16) on the layer-list decoder at one of
+    SHARED_NORM_SIZES, and, in the same process, of the framework's closest other design at equal width: the Vasolix-shaped model of --mode
+    hybrid (attention and gated-linear-attention layers).  Prefill: one prompt of --prefill-tokens tokens in one engine call.  Decode:
+    --batch sequences with --ctx cached positions each, one token per sequence per step (host batch description in, device logits out)."""
+    import numpy as np
+    import torch
+
+    mod = importlib.import_module("llm-inference-engine_b200")
+    mod.lib()
+    fed = importlib.import_module("llm-inference-engine_b200.models.fedovik")
+    sz = SHARED_NORM_SIZES[args.fedovik_size]
+    W, FF, A, L, R, M, V = sz["width"], sz["ff"], sz["attn"], sz["left"], sz["right"], sz["mlstm"], 32000
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    mlp = {"kind": "dense", "ff": FF}
+    att = {"type": "attention", "mixer": dict(heads=A["heads"], kv_heads=A["kv_heads"], dim=A["dim"], vdim=A["vdim"], scale=A["dim"] ** -0.5,
+                                              rot=dict(base=1e6, dims=A["dim"])), "mlp": mlp}
+    par = {"type": "parallel", "mixer": dict(left=dict(heads=L["heads"], kv_heads=L["kv_heads"], dim=L["dim"], vdim=L["vdim"], scale=L["dim"] ** -0.5,
+                                                       mask=dict(size=L["window"])),
+                                             right=dict(heads=R["heads"], kv_heads=R["kv_heads"], dim=R["dim"], vdim=R["vdim"], conv=4),
+                                             left_scale=0.8, right_scale=0.9), "mlp": mlp}
+    mls = {"type": "mlstm", "mixer": dict(heads=M["heads"], dim=M["dim"], vdim=M["vdim"], gate_cap=12.0), "mlp": mlp}
+    config = {"architecture": "Fedovik", "layers": [att, par, mls, par], "loop": {"start": 0, "stop": 2, "times": 2}, "norm": {"eps": 1e-5},
+              "embedding": {"scale": 1.0}, "vocab": V, "width": W}
+    runs = [0, 1, 0, 1, 2, 3]
+    gen = torch.Generator().manual_seed(7)
+
+    def rnd(*shape, std=0.02):
+        return (torch.randn(*shape, generator=gen) * std).to(torch.bfloat16)
+
+    def ones(n):
+        return torch.ones(n, dtype=torch.bfloat16)
+
+    t = {"embed": rnd(V, W, std=0.5), "final.norm": ones(W), "final.norm.b": rnd(W), "loop.in": rnd(W, 2 * W), "loop.step": rnd(2, W)}
+    for i, layer in enumerate(config["layers"]):
+        p, mx = f"l{i}.", layer["mixer"]
+        t[p + "norm1"], t[p + "norm1.b"] = ones(W), rnd(W)
+        t.update({p + "mlp.gate": rnd(FF, W), p + "mlp.up": rnd(FF, W), p + "mlp.down": rnd(W, FF)})
+
+        def attention(pre, a, sigmoid):
+            H, G, dk, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            t.update({pre + "q": rnd(H * dk, W), pre + "k": rnd(G * dk, W), pre + "v": rnd(G * dv, W), pre + "o": rnd(W, H * dv),
+                      pre + "q.b": rnd(H * dk), pre + "k.b": rnd(G * dk), pre + "v.b": rnd(G * dv)})
+            if sigmoid:
+                t.update({pre + "g": rnd(H * dv, W), pre + "o.b": rnd(W), pre + "pb": torch.full((H,), -6.0).to(torch.bfloat16)})
+            else:
+                t.update({pre + "q.norm": ones(dk), pre + "k.norm": ones(dk), pre + "r1": torch.full((H,), 0.5).to(torch.bfloat16),
+                          pre + "r2": ones(H)})
+
+        if layer["type"] == "attention":
+            attention(p + "mix.", mx, True)
+        elif layer["type"] == "parallel":
+            attention(p + "mix.left.", mx["left"], False)
+            pre, H, G, dk, dv, r = p + "mix.right.", R["heads"], R["kv_heads"], R["dim"], R["vdim"], R["rank"]
+            t.update({pre + "q": rnd(G * dk, W), pre + "k": rnd(G * dk, W), pre + "v": rnd(H * dv, W), pre + "b": rnd(H, W), pre + "o": rnd(W, H * dv),
+                      pre + "q.conv": rnd(G * dk, 4, std=0.5), pre + "k.conv": rnd(G * dk, 4, std=0.5), pre + "v.conv": rnd(H * dv, 4, std=0.5),
+                      pre + "a1": rnd(r, W), pre + "a2": rnd(H * dk, r), pre + "dt_bias": rnd(H * dk, std=1.0), pre + "A_log": torch.zeros(H, dtype=torch.bfloat16),
+                      pre + "g1": rnd(r, W), pre + "g2": rnd(H * dv, r), pre + "norm": ones(dv)})
+        else:
+            pre, H, dk, dv = p + "mix.", M["heads"], M["dim"], M["vdim"]
+            t.update({pre + "q": rnd(H * dk, W), pre + "k": rnd(H * dk, W), pre + "v": rnd(H * dv, W), pre + "g": rnd(H * dv, W), pre + "o": rnd(W, H * dv),
+                      pre + "i": rnd(H, W), pre + "f": rnd(H, W), pre + "i.b": rnd(H), pre + "f.b": torch.full((H,), 3.0).to(torch.bfloat16),
+                      pre + "norm": ones(H * dv)})
+    Tq, B, ctx = args.prefill_tokens, args.batch, args.ctx
+    page = mod.KV_PAGE_SIZE
+    per_seq = (max(Tq, ctx + args.steps + args.warmup + 8) + page - 1) // page
+    model = fed.FedovikModel(config, t, dtype="bfloat16", device=dev, max_tokens=max(Tq, B, 2048), max_seqs=max(B, 1), max_pages_per_seq=per_seq)
+    eng = model.engine
+    eng.set_pools(per_seq * max(B, 1), max(B, 1))
+    ids = torch.randint(0, V, (max(Tq, ctx + 1),), generator=gen).tolist()
+    bt = np.arange(per_seq * max(B, 1), dtype=np.int32).reshape(max(B, 1), per_seq)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    # matrix parameters a token passes, per layer (the looped layers count twice)
+    att_p = W * ((A["heads"] + A["kv_heads"]) * A["dim"] + A["kv_heads"] * A["vdim"] + 2 * A["heads"] * A["vdim"])
+    left_p = W * ((L["heads"] + L["kv_heads"]) * L["dim"] + L["kv_heads"] * L["vdim"] + L["heads"] * L["vdim"])
+    right_p = W * (2 * R["kv_heads"] * R["dim"] + 2 * R["heads"] * R["vdim"] + R["heads"] + 2 * R["rank"]) + R["rank"] * R["heads"] * (R["dim"] + R["vdim"])
+    mls_p = W * (2 * M["heads"] * M["dim"] + 3 * M["heads"] * M["vdim"] + 2 * M["heads"])
+    layer_p = [att_p + 3 * W * FF, left_p + right_p + 3 * W * FF, mls_p + 3 * W * FF, left_p + right_p + 3 * W * FF]
+    active = sum(layer_p[i] for i in runs) + 2 * 2 * W * W
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(0, gpu_uuid(dev)) as clocks:
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps, clocks.summary()
+
+    pre_ms, pre_clocks = timed(lambda: eng.forward(ids[:Tq], [0, Tq], [0], [0], bt[:1].reshape(-1), [Tq - 1]), max(3, min(args.steps, 20)), 3)
+    n_att, n_par = runs.count(0), runs.count(1) + runs.count(3)
+    attn_flops = n_att * 2.0 * A["heads"] * (A["dim"] + A["vdim"]) * sum(i + 1 for i in range(Tq)) + \
+        n_par * 2.0 * L["heads"] * (L["dim"] + L["vdim"]) * sum(min(i + 1, L["window"]) for i in range(Tq))
+    rec_flops = n_par * 2 * 3.0 * R["heads"] * R["dim"] * R["vdim"] * Tq + 2 * 2.0 * M["heads"] * M["dim"] * M["vdim"] * Tq
+    pre_tflops = (2.0 * Tq * active + attn_flops + rec_flops) / (pre_ms * 1e-3) / 1e12
+    for b in range(B):
+        eng.forward(ids[:ctx], [0, ctx], [0], [b], bt[b:b + 1].reshape(-1), [])
+    state = {"pos": ctx}
+
+    def step():
+        eng.forward(ids[:B], list(range(B + 1)), [state["pos"]] * B, list(range(B)), bt.reshape(-1), list(range(B)))
+        state["pos"] += 1
+
+    dec_ms, dec_clocks = timed(step, args.steps, max(args.warmup, 3))
+    es = 2
+    w_bytes = es * active + es * V * W
+    kv_bytes = es * B * (n_att * A["kv_heads"] * (A["dim"] + A["vdim"]) * (ctx + 1) + n_par * L["kv_heads"] * (L["dim"] + L["vdim"]) * min(ctx + 1, L["window"]))
+    st_bytes = 2 * 4 * B * (n_par * R["heads"] * R["dim"] * R["vdim"] + M["heads"] * M["dim"] * M["vdim"])
+    dec_gbs = (w_bytes + kv_bytes + st_bytes) / (dec_ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "shared-norm model prefill / decode tokens/s", "value": Tq * 1e3 / pre_ms, "unit": "tokens/s (prefill)", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "b200",
+        "config": {"model": f"Fedovik-shaped, size {args.fedovik_size}: width {W}, layers attention / parallel / mlstm / parallel, the first two twice "
+                            f"(6 layer runs), ff {FF}, window {L['window']}", "prefill_tokens": Tq, "decode_batch": B, "decode_context": ctx,
+                   "cache_policy": "weights larger than L2 at sizes m and l; no explicit flush"},
+        "fedovik": {"prefill": {"tokens_per_s": Tq * 1e3 / pre_ms, "ms": pre_ms, "tflops": pre_tflops,
+                                "frac_of_measured_bf16_sustained": pre_tflops / float(peaks.get("bf16_tflops_sustained", 1400.0)), "clocks": pre_clocks},
+                    "decode": {"tokens_per_s": B * 1e3 / dec_ms, "ms_per_step": dec_ms, "algorithmic_gb_per_s": dec_gbs,
+                               "frac_of_measured_hbm": dec_gbs / float(peaks.get("hbm_gbs", 6650.0)), "clocks": dec_clocks}},
+        "closest": None if args.no_closest else {k: v for k, v in hybrid_result(argparse.Namespace(**dict(vars(args), hybrid_size=args.fedovik_size))).items()
+                                                 if k in ("config", "prefill", "decode")},
         "e2e": "both numbers are taken through HybridDecoder.forward: host batch description in (one H2D copy per call), device logits out"}), flush=True)
 
 
@@ -1015,7 +1162,9 @@ def main():
     ap.add_argument("--requests", type=int, default=64, help="--mode serve: requests in the stream (prompts of 32..512, 32..256 new tokens)")
     ap.add_argument("--hybrid-size", default="m", choices=list(HYBRID_SIZES), help="--mode hybrid: which Vasolix-shaped model")
     ap.add_argument("--latent-size", default="m", choices=list(LATENT_SIZES), help="--mode latent: which Zefenex-shaped model")
-    ap.add_argument("--mode", default="decode", choices=["decode", "prefill", "generate", "serve", "hybrid", "latent"],
+    ap.add_argument("--fedovik-size", default="m", choices=list(SHARED_NORM_SIZES), help="--mode fedovik: which Fedovik-shaped model")
+    ap.add_argument("--no-closest", action="store_true", help="--mode fedovik: leave out the Vasolix-shaped model beside it")
+    ap.add_argument("--mode", default="decode", choices=["decode", "prefill", "generate", "serve", "hybrid", "latent", "fedovik"],
                     help="decode (default, the BASELINE metric); prefill: one pass of --prefill-tokens tokens through all layers; generate: "
                          "the whole loop through b200_generate (prompt of --prefill-tokens tokens, --new-tokens sampled tokens, host in / host out)")
     ap.add_argument("--new-tokens", type=int, default=128)
@@ -1047,6 +1196,9 @@ def main():
         return
     if args.mode == "latent":
         run_latent(args)
+        return
+    if args.mode == "fedovik":
+        run_fedovik(args)
         return
     if args.cpu_leg:  # child process of the product arm: the only place of that arm where oracle/ is loaded
         run_cpu_leg(args, cfg)

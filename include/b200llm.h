@@ -637,6 +637,43 @@ int b200_latent_attention_tiles_paged(const void *ql, const void *qr, const void
                                       int rot_dim, float scale, int window, int by_head, float *part, int part_tiles, int dtype,
                                       b200_stream_t stream);
 
+/* Scored attention (B200_MIXER_ATTN_SCORED) over paged keys [num_pages, kv_heads, B200_KV_PAGE_SIZE, dim] and values [.., vdim] of `dtype`.
+ * prep: proj [tokens, ld] holds q (heads*dim), k (kv_heads*dim), v (kv_heads*vdim) from column col0 on; b_in (optional, fp32, counted from
+ *   the same row) is added; q_norm / k_norm (optional, [dim]): RMS norm of every head with that one weight vector; the first rot_dims
+ *   dimensions of every q and k head rotate in pairs (2i, 2i+1) by pos * rot_base^(-2i/rot_dims).  q_out [tokens, heads*dim]; k and v go
+ *   to the page row of (sequence, position).
+ * attention: out[t * out_ld + h*vdim + c] = out_scale * gate * sum_j w_j v[j, g(h), c] over the keys 0 <= pos(t) - j < window (0: all
+ *   j <= pos(t)); score_j = scale * q.k_j - dist_r1[h] * ln(1 + dist_r2[h] * (pos(t) - j)) (both NULL: no penalty);
+ *   attn_weight B200_ATTN_SOFTMAX: w = softmax(score); B200_ATTN_SIGMOID: w_j = sigmoid(score_j + head_bias[h]), not normalised;
+ *   gate = sigmoid(gate_in[t * gate_ld + h*vdim + c]) (gate_in NULL: 1).  One CTA per (token, head).
+ * attention_tiles: the same on the tensor cores for tiles int4 {sequence, first packed row, rows <= 64, first position} of consecutive
+ *   tokens of one sequence (16-bit dtypes, dim and vdim of 32, 64 or 128, a penalty only with a window; B200_ERR_UNSUPPORTED otherwise). */
+int b200_scored_attn_prep_paged(const void *proj, int ld, int col0, const float *b_in, void *q_out, void *k_pool, void *v_pool,
+                                const float *q_norm, const float *k_norm, float eps, const int *tok_seq, const int *tok_pos,
+                                const int *block_table, int max_pages_per_seq, int tokens, int heads, int kv_heads, int dim, int vdim,
+                                int rot_dims, float rot_base, int dtype, b200_stream_t stream);
+int b200_scored_attention_paged(const void *q, const void *k_pool, const void *v_pool, const float *head_bias, const float *dist_r1,
+                                const float *dist_r2, const void *gate_in, int gate_ld, void *out, int out_ld, float out_scale,
+                                const int *tok_seq, const int *tok_pos, const int *block_table, int max_pages_per_seq, int tokens, int heads,
+                                int kv_heads, int dim, int vdim, float scale, int window, int attn_weight, int dtype, b200_stream_t stream);
+int b200_scored_attention_tiles_paged(const void *q, const void *k_pool, const void *v_pool, const float *head_bias, const float *dist_r1,
+                                      const float *dist_r2, const void *gate_in, int gate_ld, void *out, int out_ld, float out_scale,
+                                      const int *tiles, int n_tiles, const int *block_table, int max_pages_per_seq, int heads, int kv_heads,
+                                      int dim, int vdim, float scale, int window, int attn_weight, int dtype, b200_stream_t stream);
+/* The two column recurrences over every sequence's portion (state read from the slot unless the portion starts at position 0, written
+ * back at its end).  rec: fp32 rows per token, segments padded to multiples of four floats:
+ *   delta rule: q | k (kv_heads*dim each; unit vectors, q also / sqrt(dim)) | v (heads*vdim) | decay (heads*dim) | gate (heads*vdim, unused
+ *     here) | step (heads).   S <- diag(decay) S;  u = step * (v - S^T k);  S <- S + k u^T;  o = S^T q.
+ *   matrix memory: q | k (heads*dim each, q scaled) | v (heads*vdim) | log input gate | log forget gate (heads each).
+ *     m' = max(f + m, i);  S <- exp(f + m - m') S + exp(i - m') k v^T;  n alike with k alone;  o = S^T q (not yet divided), nq = n.q,
+ *     m_out = m' per (token, head).
+ * state fp32 [num_slots, heads, dim, vdim]; n_state [num_slots, heads, dim]; m_state [num_slots, heads]; o fp32 [tokens, heads*vdim]. */
+int b200_delta_rule_recurrent(const float *rec, float *state, float *o, const int *seq_start, const int *seq_pos0, const int *seq_slot,
+                              int n_seqs, int heads, int kv_heads, int dim, int vdim, b200_stream_t stream);
+int b200_mlstm_recurrent(const float *rec, float *state, float *n_state, float *m_state, float *o, float *nq, float *m_out,
+                         const int *seq_start, const int *seq_pos0, const int *seq_slot, int n_seqs, int heads, int dim, int vdim,
+                         b200_stream_t stream);
+
 /* ========================================== generation loop ========================================= */
 
 /* The loop LlamaModel<T>::response / generateFirstToken / generateNextToken / LMHeadAndTopKSample intend
