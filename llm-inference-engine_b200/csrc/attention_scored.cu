@@ -84,6 +84,8 @@ scored_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__
 }
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+// for weights that are rounded to 16 bits right away: hardware exponential and reciprocal (relative error ~1e-6)
+__device__ __forceinline__ float sigmoid_fast(float z) { return __fdividef(1.0f, 1.0f + __expf(-z)); }
 
 // One CTA per (token, query head).  Shared memory: q[dim] | weights[keys] | partial[key groups][vdim] | red[33].
 template <typename T>
@@ -367,8 +369,8 @@ scored_attn_mma_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, co
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int key = kt * kPageS + j * 8 + tig * 2 + e;
-                    w[e] = (key <= p_a && key >= lo_a) ? sigmoid_f(fmaf(s[j][e], sl2, hb)) : 0.0f;
-                    w[2 + e] = (key <= p_b && key >= lo_b) ? sigmoid_f(fmaf(s[j][2 + e], sl2, hb)) : 0.0f;
+                    w[e] = (key <= p_a && key >= lo_a) ? sigmoid_fast(fmaf(s[j][e], sl2, hb)) : 0.0f;
+                    w[2 + e] = (key <= p_b && key >= lo_b) ? sigmoid_fast(fmaf(s[j][2 + e], sl2, hb)) : 0.0f;
                 }
                 pf[j >> 1][(j & 1) * 2] = pack2s<T>(w[0], w[1]);
                 pf[j >> 1][(j & 1) * 2 + 1] = pack2s<T>(w[2], w[3]);

@@ -454,16 +454,24 @@ ln_residual_kernel(float *__restrict__ x, const T *__restrict__ y, const float *
 }
 
 // out[r * out_ld + c] = T(act(in[r * in_ld + gate_col + c]) * in[r * in_ld + up_col + c]): the gated feed-forward's inner row, read from
-// and written into rows that other sublayers share
-template <typename T>
+// and written into rows that other sublayers share.  grid (column blocks, rows); VEC: 16-byte pieces (every piece starts on a 16-byte boundary)
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
-gated_act_strided_kernel(const T *__restrict__ in, int in_ld, int gate_col, int up_col, T *__restrict__ out, int out_ld, int rows, int inner, int act) {
-    const size_t n = (size_t)rows * inner;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t r = i / inner;
-        const int c = (int)(i - r * inner);
-        const T *src = in + r * in_ld;
-        out[r * out_ld + c] = Elem<T>::from_f(act_apply(Elem<T>::to_f(src[gate_col + c]), act) * Elem<T>::to_f(src[up_col + c]));
+gated_act_strided_kernel(const T *__restrict__ in, int in_ld, int gate_col, int up_col, T *__restrict__ out, int out_ld, int inner, int act) {
+    constexpr int V = VEC ? Elem<T>::kVec : 1;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+    if (c >= inner) return;
+    const T *src = in + (size_t)blockIdx.y * in_ld;
+    T *dst = out + (size_t)blockIdx.y * out_ld + c;
+    if constexpr (VEC) {
+        float g[V], u[V];
+        unpack16<T>(ld_v4(src + gate_col + c), g);
+        unpack16<T>(ld_v4(src + up_col + c), u);
+#pragma unroll
+        for (int i = 0; i < V; ++i) g[i] = act_apply(g[i], act) * u[i];
+        st_v4(dst, pack16<T>(g));
+    } else {
+        dst[0] = Elem<T>::from_f(act_apply(Elem<T>::to_f(src[gate_col + c]), act) * Elem<T>::to_f(src[up_col + c]));
     }
 }
 
@@ -578,6 +586,7 @@ Carve carve(const b200_hybrid *m) {
             for (const b200_hybrid_layer_t *mx : {&l, l.side}) {
                 if (!mx) continue;
                 n_mix = std::max(n_mix, (size_t)mx->heads * std::max(mx->dim, mx->vdim));
+                n_mix = std::max(n_mix, (size_t)mx->decay_rank + mx->gate_rank + 256);  // the delta rule's two low-rank inputs as dense rows
                 n_f32 = std::max(n_f32, (size_t)mx->heads * std::max(mx->dim, mx->vdim));
                 n_rec = std::max(n_rec, (size_t)rec_cols(*mx)), n_heads = std::max(n_heads, (size_t)mx->heads);
             }
@@ -1055,7 +1064,7 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
             float *conv_state = (float *)(m->state_pool + mp.aux_off);
             const DeltaRow lay = delta_row(l.heads, l.kv_heads, l.dim, l.vdim);
             RUN(launch_delta_prep(dt, m->proj, n_in, col, l.conv_w, l.conv, conv_state, l.w_decay, l.decay_bias, l.a_log, l.decay_rank, l.w_gate2,
-                                  l.gate_rank, m->rec, d_seq, d_pos, d_start, d_pos0, d_slot, NT, l.heads, l.kv_heads, l.dim, l.vdim, st));
+                                  l.gate_rank, m->mix2, m->f32a, m->f32b, m->rec, d_seq, d_pos, d_pos0, d_slot, NT, l.heads, l.kv_heads, l.dim, l.vdim, st));
             RUN(launch_conv_state_update(dt, m->proj, n_in, col, conv_state, l.conv, 2 * l.kv_heads * l.dim + l.heads * l.vdim, d_start, d_pos0, d_slot, S, st));
             RUN(launch_delta_recurrent(m->rec, (float *)(m->state_pool + mp.state_off), m->f32b, d_start, d_pos0, d_slot, S, l.heads, l.kv_heads, l.dim,
                                        l.vdim, st));
@@ -1092,10 +1101,13 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
             col += mixer_rows(*l.side), ocol += l.side->heads * l.side->vdim;
         }
         if (l.mlp == B200_MLP_DENSE) {
-            const size_t n = (size_t)NT * l.expert_ff;
             B200_DISPATCH_DTYPE(dt, {
-                gated_act_strided_kernel<T><<<(unsigned)std::min<size_t>((n + 255) / 256, 148 * 16), 256, 0, st>>>(
-                    (const T *)m->proj, lp.n_in, col, col + l.expert_ff, (T *)m->cat + ocol, n_cat, NT, l.expert_ff, l.act);
+                constexpr int V = Elem<T>::kVec;
+                const bool vec = lp.n_in % V == 0 && col % V == 0 && l.expert_ff % V == 0 && n_cat % V == 0 && ocol % V == 0;
+                const int per = vec ? V : 1;
+                const dim3 grid((l.expert_ff / per + 255) / 256, NT);
+                if (vec) gated_act_strided_kernel<T, true><<<grid, 256, 0, st>>>((const T *)m->proj, lp.n_in, col, col + l.expert_ff, (T *)m->cat + ocol, n_cat, l.expert_ff, l.act);
+                else gated_act_strided_kernel<T, false><<<grid, 256, 0, st>>>((const T *)m->proj, lp.n_in, col, col + l.expert_ff, (T *)m->cat + ocol, n_cat, l.expert_ff, l.act);
             });
             RUN(cuda_status("gated_act_strided launch"));
         }

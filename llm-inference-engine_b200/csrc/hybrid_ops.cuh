@@ -49,15 +49,17 @@ int launch_scored_attention_tiles(int dtype, const void *q, const void *k_pool, 
                                   const int *tiles, int n_tiles, const int *block_table, int mpps, int heads, int kv_heads, int dim, int vdim,
                                   float scale, int window, int sigmoid, cudaStream_t st);
 
-// recurrent.cu: column offsets of the fp32 row per token that the prep kernels write and the recurrences read
+// recurrent.cu: column offsets of the fp32 row per token that the prep kernels write and the recurrences read.
+// launch_delta_prep scratch: lr (engine dtype) of tokens * (rank + gate_rank) elements + 256 bytes, za fp32 [tokens, heads*dim], zg fp32
+// [tokens, heads*vdim]
 struct DeltaRow { int q, k, v, decay, gate, beta, ld; };
 struct MlstmRow { int q, k, v, gi, gf, ld; };
 DeltaRow delta_row(int heads, int kv_heads, int dim, int vdim);
 MlstmRow mlstm_row(int heads, int dim, int vdim);
 int launch_delta_prep(int dtype, const void *proj, int ld, int col0, const float *conv_w, int taps, float *conv_state, const void *w_decay,
-                      const float *decay_bias, const float *a_log, int rank, const void *w_gate2, int gate_rank, float *rec, const int *tok_seq,
-                      const int *tok_pos, const int *seq_start, const int *seq_pos0, const int *seq_slot, int tokens, int heads, int kv_heads,
-                      int dim, int vdim, cudaStream_t st);
+                      const float *decay_bias, const float *a_log, int rank, const void *w_gate2, int gate_rank, void *lr, float *za, float *zg,
+                      float *rec, const int *tok_seq, const int *tok_pos, const int *seq_pos0, const int *seq_slot, int tokens, int heads,
+                      int kv_heads, int dim, int vdim, cudaStream_t st);
 int launch_conv_state_update(int dtype, const void *proj, int ld, int col0, float *conv_state, int taps, int channels, const int *seq_start,
                              const int *seq_pos0, const int *seq_slot, int n_seqs, cudaStream_t st);
 int launch_delta_recurrent(const float *rec, float *S, float *o, const int *seq_start, const int *seq_pos0, const int *seq_slot, int n_seqs,

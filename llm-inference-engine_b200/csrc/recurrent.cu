@@ -40,17 +40,18 @@ MlstmRow mlstm_row(int heads, int dim, int vdim) {
 
 // One CTA per token.  proj row: q | k (kv_heads*dim each) | v (heads*vdim) | step (heads) | decay-in (rank) | gate-in (gate_rank) from col0.
 // conv_state: fp32 [slots, taps - 1, channels]: the inputs at positions pos0 - (taps - 1) .. pos0 - 1 of the sequence in that slot.
+// Writes q, k (unit vectors), v and the step of the token's fp32 row, and the two low-rank inputs as dense rows lr_a [tokens, rank],
+// lr_g [tokens, gate_rank] for the products that follow.
 template <typename T>
 __global__ void __launch_bounds__(256)
 delta_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__restrict__ conv_w, int taps, const float *__restrict__ conv_state,
-                  const T *__restrict__ w_decay, const float *__restrict__ decay_bias, const float *__restrict__ a_log, int rank,
-                  const T *__restrict__ w_gate2, int gate_rank, float *__restrict__ rec, DeltaRow lay, const int *__restrict__ tok_seq,
-                  const int *__restrict__ tok_pos, const int *__restrict__ seq_pos0, const int *__restrict__ seq_slot, int heads, int kv_heads, int dim,
-                  int vdim) {
-    extern __shared__ float sh[];  // conv outputs [channels] | decay-in [rank] | gate-in [gate_rank]
+                  int rank, int gate_rank, T *__restrict__ lr_a, T *__restrict__ lr_g, float *__restrict__ rec, DeltaRow lay,
+                  const int *__restrict__ tok_seq, const int *__restrict__ tok_pos, const int *__restrict__ seq_pos0,
+                  const int *__restrict__ seq_slot, int heads, int kv_heads, int dim, int vdim) {
+    extern __shared__ float sh[];  // conv outputs [channels]
     const int t = blockIdx.x, s = tok_seq[t], pos = tok_pos[t], pos0 = seq_pos0[s], slot = seq_slot[s];
     const int nqk = kv_heads * dim, nv = heads * vdim, channels = 2 * nqk + nv;
-    float *cv = sh, *zin = cv + channels, *gin = zin + rank;
+    float *cv = sh;
     const float *cst = conv_state + (size_t)slot * (taps - 1) * channels;
     for (int c = threadIdx.x; c < channels; c += blockDim.x) {
         float acc = 0.0f;
@@ -64,8 +65,8 @@ delta_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__r
         cv[c] = acc * sigmoid_r(acc);
     }
     const T *row = proj + (size_t)t * ld + col0 + channels;  // step | decay-in | gate-in
-    for (int r = threadIdx.x; r < rank; r += blockDim.x) zin[r] = Elem<T>::to_f(row[heads + r]);
-    for (int r = threadIdx.x; r < gate_rank; r += blockDim.x) gin[r] = Elem<T>::to_f(row[heads + rank + r]);
+    for (int r = threadIdx.x; r < rank; r += blockDim.x) lr_a[(size_t)t * rank + r] = row[heads + r];
+    for (int r = threadIdx.x; r < gate_rank; r += blockDim.x) lr_g[(size_t)t * gate_rank + r] = row[heads + rank + r];
     __syncthreads();
     float *out = rec + (size_t)t * lay.ld;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
@@ -80,18 +81,21 @@ delta_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__r
     }
     for (int c = threadIdx.x; c < nv; c += blockDim.x) out[lay.v + c] = cv[2 * nqk + c];
     for (int h = threadIdx.x; h < heads; h += blockDim.x) out[lay.beta + h] = sigmoid_r(Elem<T>::to_f(row[h]));
-    for (int c = threadIdx.x; c < heads * dim; c += blockDim.x) {
-        float z = decay_bias ? decay_bias[c] : 0.0f;
-        const T *wr = w_decay + (size_t)c * rank;
-        for (int r = 0; r < rank; ++r) z = fmaf(Elem<T>::to_f(wr[r]), zin[r], z);
+}
+
+// za fp32 [tokens, heads*dim] = w_decay . decay-in, zg fp32 [tokens, heads*vdim] = w_gate2 . gate-in (the products of the two low-rank
+// inputs) -> the token row's decay = exp(-exp(a_log[head]) * softplus(za + bias)) and gate pre-activation (the output kernel applies
+// the sigmoid)
+__global__ void __launch_bounds__(256)
+delta_finish_kernel(const float *__restrict__ za, const float *__restrict__ zg, const float *__restrict__ decay_bias, const float *__restrict__ a_log,
+                    float *__restrict__ rec, DeltaRow lay, int heads, int dim, int vdim) {
+    const int t = blockIdx.x, nd = heads * dim, nv = heads * vdim;
+    float *out = rec + (size_t)t * lay.ld;
+    for (int c = threadIdx.x; c < nd; c += blockDim.x) {
+        const float z = za[(size_t)t * nd + c] + (decay_bias ? decay_bias[c] : 0.0f);
         out[lay.decay + c] = expf(-expf(a_log[c / dim]) * softplus_r(z));
     }
-    for (int c = threadIdx.x; c < nv; c += blockDim.x) {
-        float z = 0.0f;
-        const T *wr = w_gate2 + (size_t)c * gate_rank;
-        for (int r = 0; r < gate_rank; ++r) z = fmaf(Elem<T>::to_f(wr[r]), gin[r], z);
-        out[lay.gate + c] = z;  // the output kernel applies the sigmoid
-    }
+    for (int c = threadIdx.x; c < nv; c += blockDim.x) out[lay.gate + c] = zg[(size_t)t * nv + c];
 }
 
 // After the convolutions have read it: the state's rows move up by the portion's length and its last inputs come in.  One CTA per
@@ -139,22 +143,37 @@ mlstm_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__r
     }
 }
 
-// grid (column tiles, heads, sequences); blockDim = CB * LANES threads.  A column's rows r = sub * RPT + i live in registers of lane `sub`.
-// MODE 0 (delta): per token k, q, decay [dim] and beta;  MODE 1 (matrix memory): per token k, q [dim] and the log gates.
-// Shared memory per staged token: kq[3 * DP] (k | q | decay, DP = RPT * LANES, zero beyond dim) | two scalars; kTB tokens per stage.
+// grid (column tiles, heads, sequences); blockDim = CB * LANES threads.  A column's rows r = sub * RPT + i (RPT = DP / LANES) live in the
+// registers of lane `sub` of the column's LANES adjacent threads; dot products over the rows end in a butterfly over those lanes.  The
+// host picks LANES by how many columns the batch has: one long prompt spreads every column over many threads (the token loop is
+// sequential, its length per token is RPT), a decode batch of many sequences keeps whole columns in one thread.
+// MODE 0 (delta): per token k, q, decay [dim] and the step;  MODE 1 (matrix memory): per token k, q [dim] and the two log gates.
+// Shared memory, two stages of kRecTB tokens: per token [NV * DP key-side values (zero beyond dim) | 4 scalars], then v [kRecTB][CB].  The
+// next stage arrives by cp.async while the current one is consumed.
 constexpr int kRecTB = 8;
 
-template <int RPT, int LANES, int MODE>
-__global__ void __launch_bounds__(128)
+__device__ __forceinline__ void cp_async4_r(void *smem, const void *gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async16_r(void *smem, const void *gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_r() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait_r() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int DP, int LANES, int MODE>
+__global__ void __launch_bounds__(256)
 column_recurrence_kernel(const float *__restrict__ rec, int rec_ld, int q_off, int k_off, int v_off, int a_off, int b_off,
                          float *__restrict__ S, float *__restrict__ n_state, float *__restrict__ m_state, float *__restrict__ o,
                          float *__restrict__ nq_out, float *__restrict__ m_out, const int *__restrict__ seq_start,
                          const int *__restrict__ seq_pos0, const int *__restrict__ seq_slot, int heads, int kv_heads, int dim, int vdim) {
-    constexpr int DP = RPT * LANES, NV = MODE == 0 ? 3 : 2;
-    extern __shared__ __align__(16) float stage[];  // [kRecTB][NV * DP + 4] | v [kRecTB][CB]
+    constexpr int RPT = DP / LANES, NV = MODE == 0 ? 3 : 2, TS = NV * DP + 4;
+    static_assert(RPT >= 4 && RPT % 4 == 0 && RPT <= 128, "rows per thread");
+    extern __shared__ __align__(16) float stage[];  // [2][kRecTB][TS] | v [2][kRecTB][CB]
     const int CB = blockDim.x / LANES;
-    constexpr int TS = NV * DP + 4;
-    float *vs = stage + kRecTB * TS;
+    float *vs = stage + 2 * kRecTB * TS;
     const int s = blockIdx.z, h = blockIdx.y, g = h / (heads / kv_heads);
     const int t0 = seq_start[s], len = seq_start[s + 1] - t0;
     if (len <= 0) return;
@@ -166,6 +185,43 @@ column_recurrence_kernel(const float *__restrict__ rec, int rec_ld, int q_off, i
     const int r0 = sub * RPT;
     float *Sp = S + ((size_t)slot * heads + h) * dim * vdim;
     float *np = MODE == 1 ? n_state + ((size_t)slot * heads + h) * dim : nullptr;
+    // 16-byte copies when every source segment starts on a 16-byte boundary (the row's segments do; a head's part of one does if dim % 4 == 0)
+    const bool v16 = dim % 4 == 0 && rec_ld % 4 == 0 && ((q_off | k_off | a_off) & 3) == 0 && (reinterpret_cast<size_t>(rec) & 15) == 0;
+
+    for (int i = threadIdx.x; i < 2 * kRecTB * TS; i += blockDim.x) stage[i] = 0.0f;  // the rows beyond dim stay zero for good
+    __syncthreads();
+    auto fetch = [&](int c0, int buf) {  // tokens c0 .. c0 + kRecTB - 1 of the portion into stage `buf`
+        const int nt = min(kRecTB, len - c0);
+        float *dst = stage + buf * kRecTB * TS;
+        if (v16) {
+            const int per = dim / 4;
+            for (int i = threadIdx.x; i < nt * NV * per; i += blockDim.x) {
+                const int tt = i / (NV * per), w = i - tt * (NV * per), which = w / per, r = (w - which * per) * 4;
+                const float *row = rec + (size_t)(t0 + c0 + tt) * rec_ld;
+                const float *src = which == 0 ? row + k_off + g * dim + r : (which == 1 ? row + q_off + g * dim + r : row + a_off + h * dim + r);
+                cp_async16_r(dst + tt * TS + which * DP + r, src);
+            }
+        } else {
+            for (int i = threadIdx.x; i < nt * NV * dim; i += blockDim.x) {
+                const int tt = i / (NV * dim), w = i - tt * (NV * dim), which = w / dim, r = w - which * dim;
+                const float *row = rec + (size_t)(t0 + c0 + tt) * rec_ld;
+                const float *src = which == 0 ? row + k_off + g * dim + r : (which == 1 ? row + q_off + g * dim + r : row + a_off + h * dim + r);
+                cp_async4_r(dst + tt * TS + which * DP + r, src);
+            }
+        }
+        for (int i = threadIdx.x; i < nt * 2; i += blockDim.x) {
+            const int tt = i >> 1, w = i & 1;
+            const float *row = rec + (size_t)(t0 + c0 + tt) * rec_ld;
+            cp_async4_r(dst + tt * TS + NV * DP + w, MODE == 0 ? row + b_off + h : (w == 0 ? row + a_off + h : row + b_off + h));
+        }
+        for (int i = threadIdx.x; i < nt * CB; i += blockDim.x) {
+            const int tt = i / CB, cc = i - tt * CB, c = blockIdx.x * CB + cc;
+            if (c < vdim) cp_async4_r(vs + (buf * kRecTB + tt) * CB + cc, rec + (size_t)(t0 + c0 + tt) * rec_ld + v_off + h * vdim + c);
+            else vs[(buf * kRecTB + tt) * CB + cc] = 1.0f;  // the normaliser's column: its value is 1
+        }
+    };
+    fetch(0, 0);
+    cp_async_commit_r();
 
     float st[RPT];
 #pragma unroll
@@ -175,42 +231,29 @@ column_recurrence_kernel(const float *__restrict__ rec, int rec_ld, int q_off, i
     }
     float m = (MODE == 1 && pos0 > 0) ? m_state[(size_t)slot * heads + h] : 0.0f;
 
-    for (int c0 = 0; c0 < len; c0 += kRecTB) {
+    for (int c0 = 0, buf = 0; c0 < len; c0 += kRecTB, buf ^= 1) {
         const int nt = min(kRecTB, len - c0);
-        __syncthreads();  // the previous stage has been consumed
-        for (int i = threadIdx.x; i < nt * NV * DP; i += blockDim.x) {
-            const int tt = i / (NV * DP), w = i - tt * (NV * DP), which = w / DP, r = w - which * DP;
-            const float *row = rec + (size_t)(t0 + c0 + tt) * rec_ld;
-            float x = 0.0f;
-            if (r < dim) x = which == 0 ? row[k_off + g * dim + r] : (which == 1 ? row[q_off + g * dim + r] : row[a_off + h * dim + r]);
-            stage[tt * TS + w] = x;
-        }
-        for (int i = threadIdx.x; i < nt * 2; i += blockDim.x) {
-            const int tt = i >> 1, w = i & 1;
-            const float *row = rec + (size_t)(t0 + c0 + tt) * rec_ld;
-            stage[tt * TS + NV * DP + w] = MODE == 0 ? row[b_off + h] : (w == 0 ? row[a_off + h] : row[b_off + h]);
-        }
-        for (int i = threadIdx.x; i < nt * CB; i += blockDim.x) {
-            const int tt = i / CB, c = blockIdx.x * CB + (i - tt * CB);
-            vs[tt * CB + (i - tt * CB)] = c < vdim ? rec[(size_t)(t0 + c0 + tt) * rec_ld + v_off + h * vdim + c] : 1.0f;
-        }
+        if (c0 + kRecTB < len) fetch(c0 + kRecTB, buf ^ 1);
+        cp_async_commit_r();
+        cp_async_wait_r<1>();
         __syncthreads();
+        const float *sb = stage + buf * kRecTB * TS;
         for (int tt = 0; tt < nt; ++tt) {
-            const float4 *kp = reinterpret_cast<const float4 *>(stage + tt * TS + r0);
-            const float4 *qp = reinterpret_cast<const float4 *>(stage + tt * TS + DP + r0);
-            const float v = vs[tt * CB + cl];
-            float out0 = 0.0f, out1 = 0.0f;
+            const float4 *kp = reinterpret_cast<const float4 *>(sb + tt * TS + r0);
+            const float4 *qp = reinterpret_cast<const float4 *>(sb + tt * TS + DP + r0);
+            const float v = vs[(buf * kRecTB + tt) * CB + cl];
+            float e0 = 0.0f, e1 = 0.0f, e2 = 0.0f, e3 = 0.0f;  // four chains per dot product: the adds' latency is the loop's critical path
             if (MODE == 0) {
-                const float4 *gp = reinterpret_cast<const float4 *>(stage + tt * TS + 2 * DP + r0);
-                const float beta = stage[tt * TS + NV * DP];
-                float d0 = 0.0f, d1 = 0.0f;
+                const float4 *gp = reinterpret_cast<const float4 *>(sb + tt * TS + 2 * DP + r0);
+                const float beta = sb[tt * TS + NV * DP];
+                float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
 #pragma unroll
                 for (int i = 0; i < RPT; i += 4) {
                     const float4 kk = kp[i >> 2], gg = gp[i >> 2];
                     st[i] *= gg.x, st[i + 1] *= gg.y, st[i + 2] *= gg.z, st[i + 3] *= gg.w;
-                    d0 = fmaf(kk.x, st[i], d0), d1 = fmaf(kk.y, st[i + 1], d1), d0 = fmaf(kk.z, st[i + 2], d0), d1 = fmaf(kk.w, st[i + 3], d1);
+                    d0 = fmaf(kk.x, st[i], d0), d1 = fmaf(kk.y, st[i + 1], d1), d2 = fmaf(kk.z, st[i + 2], d2), d3 = fmaf(kk.w, st[i + 3], d3);
                 }
-                float dot = d0 + d1;
+                float dot = (d0 + d1) + (d2 + d3);
 #pragma unroll
                 for (int w = LANES >> 1; w > 0; w >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, w);
                 const float u = beta * (v - dot);
@@ -218,10 +261,10 @@ column_recurrence_kernel(const float *__restrict__ rec, int rec_ld, int q_off, i
                 for (int i = 0; i < RPT; i += 4) {
                     const float4 kk = kp[i >> 2], qq = qp[i >> 2];
                     st[i] = fmaf(kk.x, u, st[i]), st[i + 1] = fmaf(kk.y, u, st[i + 1]), st[i + 2] = fmaf(kk.z, u, st[i + 2]), st[i + 3] = fmaf(kk.w, u, st[i + 3]);
-                    out0 = fmaf(qq.x, st[i], out0), out1 = fmaf(qq.y, st[i + 1], out1), out0 = fmaf(qq.z, st[i + 2], out0), out1 = fmaf(qq.w, st[i + 3], out1);
+                    e0 = fmaf(qq.x, st[i], e0), e1 = fmaf(qq.y, st[i + 1], e1), e2 = fmaf(qq.z, st[i + 2], e2), e3 = fmaf(qq.w, st[i + 3], e3);
                 }
             } else {
-                const float gi = stage[tt * TS + NV * DP], gf = stage[tt * TS + NV * DP + 1];
+                const float gi = sb[tt * TS + NV * DP], gf = sb[tt * TS + NV * DP + 1];
                 const float m_new = fmaxf(gf + m, gi);
                 const float a = expf(gf + m - m_new), bv = expf(gi - m_new) * v;
                 m = m_new;
@@ -229,10 +272,10 @@ column_recurrence_kernel(const float *__restrict__ rec, int rec_ld, int q_off, i
                 for (int i = 0; i < RPT; i += 4) {
                     const float4 kk = kp[i >> 2], qq = qp[i >> 2];
                     st[i] = fmaf(a, st[i], kk.x * bv), st[i + 1] = fmaf(a, st[i + 1], kk.y * bv), st[i + 2] = fmaf(a, st[i + 2], kk.z * bv), st[i + 3] = fmaf(a, st[i + 3], kk.w * bv);
-                    out0 = fmaf(qq.x, st[i], out0), out1 = fmaf(qq.y, st[i + 1], out1), out0 = fmaf(qq.z, st[i + 2], out0), out1 = fmaf(qq.w, st[i + 3], out1);
+                    e0 = fmaf(qq.x, st[i], e0), e1 = fmaf(qq.y, st[i + 1], e1), e2 = fmaf(qq.z, st[i + 2], e2), e3 = fmaf(qq.w, st[i + 3], e3);
                 }
             }
-            float out = out0 + out1;
+            float out = (e0 + e1) + (e2 + e3);
 #pragma unroll
             for (int w = LANES >> 1; w > 0; w >>= 1) out += __shfl_xor_sync(0xffffffffu, out, w);
             if (active && sub == 0) {
@@ -241,6 +284,7 @@ column_recurrence_kernel(const float *__restrict__ rec, int rec_ld, int q_off, i
                 else o[(tok * heads + h) * vdim + col] = out;
             }
         }
+        __syncthreads();  // the stage is consumed: the fetch after next may overwrite it
     }
     if (!active) return;
 #pragma unroll
@@ -279,22 +323,32 @@ head_output_kernel(const float *__restrict__ o, const float *__restrict__ nq, co
     }
 }
 
-template <int RPT, int LANES, int MODE>
+template <int DP, int LANES, int MODE>
 static int launch_colrec_t(const float *rec, int rec_ld, int q_off, int k_off, int v_off, int a_off, int b_off, float *S, float *n_state,
                            float *m_state, float *o, float *nq, float *m_out, const int *seq_start, const int *seq_pos0, const int *seq_slot,
                            int n_seqs, int heads, int kv_heads, int dim, int vdim, cudaStream_t st) {
     const int ncols = MODE == 1 ? vdim + 1 : vdim;
-    // few sequences: narrow column tiles spread a portion's columns over more SMs
-    int cb = 128 / LANES;
-    while (cb > 32 / LANES && cb > 8 && (long long)((ncols + cb - 1) / cb) * heads * n_seqs < 2 * 148) cb >>= 1;
-    if (cb * LANES < 32) cb = 32 / LANES;
+    // every CTA stages its head's key-side vectors for itself, so CTAs are as wide as the batch allows while about a hundred of them remain
+    const long long threads = (long long)ncols * LANES * heads * n_seqs;
+    int block = 256;
+    while (block > 32 && block > LANES && threads / block < 100) block >>= 1;
+    if (block < LANES) block = LANES;
+    const int cb = block / LANES;
     constexpr int NV = MODE == 0 ? 3 : 2;
-    const size_t smem = ((size_t)kRecTB * (NV * RPT * LANES + 4) + (size_t)kRecTB * cb) * sizeof(float);
-    auto kern = column_recurrence_kernel<RPT, LANES, MODE>;
+    const size_t smem = ((size_t)2 * kRecTB * (NV * DP + 4) + (size_t)2 * kRecTB * cb) * sizeof(float);
+    auto kern = column_recurrence_kernel<DP, LANES, MODE>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     kern<<<dim3((ncols + cb - 1) / cb, heads, n_seqs), cb * LANES, smem, st>>>(rec, rec_ld, q_off, k_off, v_off, a_off, b_off, S, n_state, m_state, o, nq,
                                                                              m_out, seq_start, seq_pos0, seq_slot, heads, kv_heads, dim, vdim);
     return cuda_status("column_recurrence launch");
+}
+
+// how many lanes share a column: as many as it takes to give the device about two warps per SM, within what the padded key size allows
+// (at least 4 rows per lane for the 16-byte shared-memory reads, at most 128 for the registers)
+static int pick_lanes(int dp, long long columns) {
+    int lanes = dp > 128 ? dp / 128 : 1;
+    while (lanes < 16 && dp / (2 * lanes) >= 4 && columns * lanes < 148LL * 2 * 32) lanes *= 2;
+    return lanes;
 }
 
 template <int MODE>
@@ -302,35 +356,52 @@ static int launch_colrec(const float *rec, int rec_ld, int q_off, int k_off, int
                          float *m_state, float *o, float *nq, float *m_out, const int *seq_start, const int *seq_pos0, const int *seq_slot,
                          int n_seqs, int heads, int kv_heads, int dim, int vdim, cudaStream_t st) {
     if (n_seqs == 0) return B200_OK;
-#define B200_COLREC(R, L) \
-    return launch_colrec_t<R, L, MODE>(rec, rec_ld, q_off, k_off, v_off, a_off, b_off, S, n_state, m_state, o, nq, m_out, seq_start, seq_pos0, seq_slot, n_seqs, heads, kv_heads, dim, vdim, st)
-    if (dim <= 16) B200_COLREC(16, 1);
-    if (dim <= 32) B200_COLREC(32, 1);
-    if (dim <= 48) B200_COLREC(48, 1);
-    if (dim <= 64) B200_COLREC(64, 1);
-    if (dim <= 96) B200_COLREC(96, 1);
-    if (dim <= 128) B200_COLREC(128, 1);
-    if (dim <= 256) B200_COLREC(128, 2);
-    if (dim <= 512) B200_COLREC(128, 4);
+    if (dim > 512) {
+        set_error("column recurrence: key size %d above 512", dim);
+        return B200_ERR_UNSUPPORTED;
+    }
+    const int dp = dim <= 16 ? 16 : (dim <= 32 ? 32 : (dim <= 64 ? 64 : (dim <= 128 ? 128 : (dim <= 256 ? 256 : 512))));
+    const int lanes = pick_lanes(dp, (long long)n_seqs * heads * (vdim + MODE));
+#define B200_COLREC(D, L)  \
+    if (dp == D && lanes == L) \
+        return launch_colrec_t<D, L, MODE>(rec, rec_ld, q_off, k_off, v_off, a_off, b_off, S, n_state, m_state, o, nq, m_out, seq_start, seq_pos0, seq_slot, n_seqs, heads, kv_heads, dim, vdim, st)
+    B200_COLREC(16, 1); B200_COLREC(16, 2); B200_COLREC(16, 4);
+    B200_COLREC(32, 1); B200_COLREC(32, 2); B200_COLREC(32, 4); B200_COLREC(32, 8);
+    B200_COLREC(64, 1); B200_COLREC(64, 2); B200_COLREC(64, 4); B200_COLREC(64, 8); B200_COLREC(64, 16);
+    B200_COLREC(128, 1); B200_COLREC(128, 2); B200_COLREC(128, 4); B200_COLREC(128, 8); B200_COLREC(128, 16);
+    B200_COLREC(256, 2); B200_COLREC(256, 4); B200_COLREC(256, 8); B200_COLREC(256, 16);
+    B200_COLREC(512, 4); B200_COLREC(512, 8); B200_COLREC(512, 16);
 #undef B200_COLREC
-    set_error("column recurrence: key size %d above 512", dim);
+    set_error("column recurrence: no kernel for key size %d with %d lanes", dim, lanes);
     return B200_ERR_UNSUPPORTED;
 }
 
 int launch_delta_prep(int dtype, const void *proj, int ld, int col0, const float *conv_w, int taps, float *conv_state, const void *w_decay,
-                      const float *decay_bias, const float *a_log, int rank, const void *w_gate2, int gate_rank, float *rec, const int *tok_seq,
-                      const int *tok_pos, const int *seq_start, const int *seq_pos0, const int *seq_slot, int tokens, int heads, int kv_heads,
-                      int dim, int vdim, cudaStream_t st) {
+                      const float *decay_bias, const float *a_log, int rank, const void *w_gate2, int gate_rank, void *lr, float *za, float *zg,
+                      float *rec, const int *tok_seq, const int *tok_pos, const int *seq_pos0, const int *seq_slot, int tokens, int heads,
+                      int kv_heads, int dim, int vdim, cudaStream_t st) {
     if (tokens == 0) return B200_OK;
     const DeltaRow lay = delta_row(heads, kv_heads, dim, vdim);
-    const size_t smem = ((size_t)2 * kv_heads * dim + heads * vdim + rank + gate_rank) * sizeof(float);
+    const size_t smem = ((size_t)2 * kv_heads * dim + heads * vdim) * sizeof(float), es = dtype == B200_F32 ? 4 : 2;
+    void *lr_a = lr, *lr_g = (char *)lr + (((size_t)tokens * rank * es + 255) & ~(size_t)255);
     B200_DISPATCH_DTYPE(dtype, {
         if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        delta_prep_kernel<T><<<tokens, 256, smem, st>>>((const T *)proj, ld, col0, conv_w, taps, conv_state, (const T *)w_decay, decay_bias, a_log, rank,
-                                                       (const T *)w_gate2, gate_rank, rec, lay, tok_seq, tok_pos, seq_pos0, seq_slot, heads, kv_heads, dim,
-                                                       vdim);
+        delta_prep_kernel<T><<<tokens, 256, smem, st>>>((const T *)proj, ld, col0, conv_w, taps, conv_state, rank, gate_rank, (T *)lr_a, (T *)lr_g, rec, lay,
+                                                       tok_seq, tok_pos, seq_pos0, seq_slot, heads, kv_heads, dim, vdim);
     });
-    return cuda_status("delta_prep launch");
+    int rc = cuda_status("delta_prep launch");
+    if (rc != B200_OK) return rc;
+    // the second halves of the two low-rank projections, fp32 out: tensor cores for 16-bit engines, the fp32 kernel otherwise
+    const void *ws[2] = {w_decay, w_gate2}, *xs[2] = {lr_a, lr_g};
+    float *zs[2] = {za, zg};
+    const int ns[2] = {heads * dim, heads * vdim}, ks[2] = {rank, gate_rank};
+    for (int i = 0; i < 2; ++i) {
+        rc = launch_dense_f32out(dtype, xs[i], ws[i], zs[i], tokens, ns[i], ks[i], st);
+        if (rc == B200_ERR_UNSUPPORTED) rc = launch_proj_f32(dtype, xs[i], ks[i], dtype, ws[i], nullptr, zs[i], ns[i], tokens, ns[i], ks[i], st);
+        if (rc != B200_OK) return rc;
+    }
+    delta_finish_kernel<<<tokens, 256, 0, st>>>(za, zg, decay_bias, a_log, rec, lay, heads, dim, vdim);
+    return cuda_status("delta_finish launch");
 }
 
 int launch_conv_state_update(int dtype, const void *proj, int ld, int col0, float *conv_state, int taps, int channels, const int *seq_start,
