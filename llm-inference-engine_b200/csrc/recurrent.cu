@@ -15,6 +15,7 @@
 #include "hybrid_ops.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace b200 {
 
@@ -143,14 +144,16 @@ mlstm_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__r
     }
 }
 
-// grid (column tiles, heads, sequences); blockDim = CB * LANES threads.  A column's rows r = sub * RPT + i (RPT = DP / LANES) live in the
-// registers of lane `sub` of the column's LANES adjacent threads; dot products over the rows end in a butterfly over those lanes.  The
-// host picks LANES by how many columns the batch has: one long prompt spreads every column over many threads (the token loop is
-// sequential, its length per token is RPT), a decode batch of many sequences keeps whole columns in one thread.
+// grid (column tiles, heads, sequences); blockDim = CB / CPT * LANES threads.  A thread holds a tile of the state in registers: CPT adjacent
+// columns x RPT = DP / LANES rows, the rows dealt out over the LANES adjacent threads of a column group in fours (lane `sub` holds rows
+// 4 * (sub + LANES * j) .. + 3, so the lanes read consecutive 16-byte pieces of a staged vector: no bank conflicts).  A staged key-side value
+// is read once for the thread's CPT columns, the columns' chains run side by side, and dot products over the rows end in a butterfly over
+// the lanes.  The host picks LANES by how many columns the batch has: one long prompt spreads every column group over many threads (the
+// token loop is sequential, its length per token is RPT), a decode batch of many sequences keeps longer pieces of a column in one thread.
 // MODE 0 (delta): per token k, q, decay [dim] and the step;  MODE 1 (matrix memory): per token k, q [dim] and the two log gates.
 // Shared memory, two stages of kRecTB tokens: per token [NV * DP key-side values (zero beyond dim) | 4 scalars], then v [kRecTB][CB].  The
 // next stage arrives by cp.async while the current one is consumed.
-constexpr int kRecTB = 8;
+constexpr int kRecTB = 16;
 
 __device__ __forceinline__ void cp_async4_r(void *smem, const void *gmem) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -163,71 +166,80 @@ __device__ __forceinline__ void cp_async16_r(void *smem, const void *gmem) {
 __device__ __forceinline__ void cp_async_commit_r() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait_r() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int DP, int LANES, int MODE>
+template <int DP, int LANES, int CPT, int MODE>
 __global__ void __launch_bounds__(256)
 column_recurrence_kernel(const float *__restrict__ rec, int rec_ld, int q_off, int k_off, int v_off, int a_off, int b_off,
                          float *__restrict__ S, float *__restrict__ n_state, float *__restrict__ m_state, float *__restrict__ o,
                          float *__restrict__ nq_out, float *__restrict__ m_out, const int *__restrict__ seq_start,
                          const int *__restrict__ seq_pos0, const int *__restrict__ seq_slot, int heads, int kv_heads, int dim, int vdim) {
     constexpr int RPT = DP / LANES, NV = MODE == 0 ? 3 : 2, TS = NV * DP + 4;
-    static_assert(RPT >= 4 && RPT % 4 == 0 && RPT <= 128, "rows per thread");
+    static_assert(RPT >= 4 && RPT % 4 == 0 && RPT * CPT <= 128, "state tile per thread");
     extern __shared__ __align__(16) float stage[];  // [2][kRecTB][TS] | v [2][kRecTB][CB]
-    const int CB = blockDim.x / LANES;
+    const int CB = blockDim.x / LANES * CPT;  // columns of this CTA
     float *vs = stage + 2 * kRecTB * TS;
     const int s = blockIdx.z, h = blockIdx.y, g = h / (heads / kv_heads);
     const int t0 = seq_start[s], len = seq_start[s + 1] - t0;
     if (len <= 0) return;
     const int pos0 = seq_pos0[s], slot = seq_slot[s];
     const int ncols = MODE == 1 ? vdim + 1 : vdim;
-    const int cl = threadIdx.x / LANES, sub = threadIdx.x % LANES;
+    const int cl = threadIdx.x / LANES * CPT, sub = threadIdx.x % LANES;  // first column within the CTA, lane within the column group
     const int col = blockIdx.x * CB + cl;
-    const bool active = col < ncols, is_n = MODE == 1 && col == vdim;
-    const int r0 = sub * RPT;
+    auto row_of = [&](int i) { return 4 * (sub + LANES * (i >> 2)) + (i & 3); };  // the row that register row i of this lane holds
     float *Sp = S + ((size_t)slot * heads + h) * dim * vdim;
     float *np = MODE == 1 ? n_state + ((size_t)slot * heads + h) * dim : nullptr;
     // 16-byte copies when every source segment starts on a 16-byte boundary (the row's segments do; a head's part of one does if dim % 4 == 0)
     const bool v16 = dim % 4 == 0 && rec_ld % 4 == 0 && ((q_off | k_off | a_off) & 3) == 0 && (reinterpret_cast<size_t>(rec) & 15) == 0;
 
-    for (int i = threadIdx.x; i < 2 * kRecTB * TS; i += blockDim.x) stage[i] = 0.0f;  // the rows beyond dim stay zero for good
-    __syncthreads();
+    if (dim < DP) {  // the rows beyond dim are zeroed once and never copied over
+        const int pad = DP - dim;
+        for (int i = threadIdx.x; i < 2 * kRecTB * NV * pad; i += blockDim.x) {
+            const int tt = i / (NV * pad), w = i - tt * (NV * pad), which = w / pad;
+            stage[tt * TS + which * DP + dim + (w - which * pad)] = 0.0f;
+        }
+        __syncthreads();
+    }
+    // a thread copies the same piece of every token of a stage: the split of its index into (vector, row) is done once per stage
     auto fetch = [&](int c0, int buf) {  // tokens c0 .. c0 + kRecTB - 1 of the portion into stage `buf`
         const int nt = min(kRecTB, len - c0);
         float *dst = stage + buf * kRecTB * TS;
-        if (v16) {
-            const int per = dim / 4;
-            for (int i = threadIdx.x; i < nt * NV * per; i += blockDim.x) {
-                const int tt = i / (NV * per), w = i - tt * (NV * per), which = w / per, r = (w - which * per) * 4;
-                const float *row = rec + (size_t)(t0 + c0 + tt) * rec_ld;
-                const float *src = which == 0 ? row + k_off + g * dim + r : (which == 1 ? row + q_off + g * dim + r : row + a_off + h * dim + r);
-                cp_async16_r(dst + tt * TS + which * DP + r, src);
-            }
-        } else {
-            for (int i = threadIdx.x; i < nt * NV * dim; i += blockDim.x) {
-                const int tt = i / (NV * dim), w = i - tt * (NV * dim), which = w / dim, r = w - which * dim;
-                const float *row = rec + (size_t)(t0 + c0 + tt) * rec_ld;
-                const float *src = which == 0 ? row + k_off + g * dim + r : (which == 1 ? row + q_off + g * dim + r : row + a_off + h * dim + r);
-                cp_async4_r(dst + tt * TS + which * DP + r, src);
+        const float *row0 = rec + (size_t)(t0 + c0) * rec_ld;
+        const int per = v16 ? dim / 4 : dim;
+        for (int j = threadIdx.x; j < NV * per; j += blockDim.x) {
+            const int which = j / per, r = (j - which * per) * (v16 ? 4 : 1);
+            const float *src = row0 + (which == 0 ? k_off + g * dim : (which == 1 ? q_off + g * dim : a_off + h * dim)) + r;
+            float *d = dst + which * DP + r;
+            if (v16) {
+                for (int tt = 0; tt < nt; ++tt) cp_async16_r(d + tt * TS, src + (size_t)tt * rec_ld);
+            } else {
+                for (int tt = 0; tt < nt; ++tt) cp_async4_r(d + tt * TS, src + (size_t)tt * rec_ld);
             }
         }
-        for (int i = threadIdx.x; i < nt * 2; i += blockDim.x) {
-            const int tt = i >> 1, w = i & 1;
-            const float *row = rec + (size_t)(t0 + c0 + tt) * rec_ld;
-            cp_async4_r(dst + tt * TS + NV * DP + w, MODE == 0 ? row + b_off + h : (w == 0 ? row + a_off + h : row + b_off + h));
+        if (threadIdx.x < 2) {
+            const int w = threadIdx.x;
+            const float *src = row0 + (MODE == 0 ? b_off + h : (w == 0 ? a_off + h : b_off + h));
+            for (int tt = 0; tt < nt; ++tt) cp_async4_r(dst + tt * TS + NV * DP + w, src + (size_t)tt * rec_ld);
         }
-        for (int i = threadIdx.x; i < nt * CB; i += blockDim.x) {
-            const int tt = i / CB, cc = i - tt * CB, c = blockIdx.x * CB + cc;
-            if (c < vdim) cp_async4_r(vs + (buf * kRecTB + tt) * CB + cc, rec + (size_t)(t0 + c0 + tt) * rec_ld + v_off + h * vdim + c);
-            else vs[(buf * kRecTB + tt) * CB + cc] = 1.0f;  // the normaliser's column: its value is 1
+        for (int cc = threadIdx.x; cc < CB; cc += blockDim.x) {
+            const int c = blockIdx.x * CB + cc;
+            for (int tt = 0; tt < nt; ++tt) {
+                if (c < vdim) cp_async4_r(vs + (buf * kRecTB + tt) * CB + cc, row0 + (size_t)tt * rec_ld + v_off + h * vdim + c);
+                else vs[(buf * kRecTB + tt) * CB + cc] = 1.0f;  // the normaliser's column: its value is 1
+            }
         }
     };
     fetch(0, 0);
     cp_async_commit_r();
 
-    float st[RPT];
+    // st[i][c]: row row_of(i), column col + c.  Column vdim of the matrix memory is the normaliser n
+    float st[RPT][CPT];
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
-        const int r = r0 + i;
-        st[i] = (pos0 > 0 && active && r < dim) ? (is_n ? np[r] : Sp[(size_t)r * vdim + col]) : 0.0f;
+        const int r = row_of(i);
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+            const int cc = col + c;
+            st[i][c] = (pos0 > 0 && cc < ncols && r < dim) ? ((MODE == 1 && cc == vdim) ? np[r] : Sp[(size_t)r * vdim + cc]) : 0.0f;
+        }
     }
     float m = (MODE == 1 && pos0 > 0) ? m_state[(size_t)slot * heads + h] : 0.0f;
 
@@ -238,64 +250,102 @@ column_recurrence_kernel(const float *__restrict__ rec, int rec_ld, int q_off, i
         cp_async_wait_r<1>();
         __syncthreads();
         const float *sb = stage + buf * kRecTB * TS;
-        for (int tt = 0; tt < nt; ++tt) {
-            const float4 *kp = reinterpret_cast<const float4 *>(sb + tt * TS + r0);
-            const float4 *qp = reinterpret_cast<const float4 *>(sb + tt * TS + DP + r0);
-            const float v = vs[(buf * kRecTB + tt) * CB + cl];
-            float e0 = 0.0f, e1 = 0.0f, e2 = 0.0f, e3 = 0.0f;  // four chains per dot product: the adds' latency is the loop's critical path
+#pragma unroll 4
+        for (int tt = 0; tt < nt; ++tt) {  // unrolled: a token's read-out reduction overlaps the next token's first pass
+            // piece j of a lane: float4 number sub + LANES * j of the staged vector
+            const float4 *kp = reinterpret_cast<const float4 *>(sb + tt * TS) + sub;
+            const float4 *qp = reinterpret_cast<const float4 *>(sb + tt * TS + DP) + sub;
+            float v[CPT], out[CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) v[c] = vs[(buf * kRecTB + tt) * CB + cl + c], out[c] = 0.0f;
             if (MODE == 0) {
-                const float4 *gp = reinterpret_cast<const float4 *>(sb + tt * TS + 2 * DP + r0);
+                const float4 *gp = reinterpret_cast<const float4 *>(sb + tt * TS + 2 * DP) + sub;
                 const float beta = sb[tt * TS + NV * DP];
-                float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+                float dot[CPT];
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) dot[c] = 0.0f;
+                float kr[RPT];  // the key stays in registers for the second pass
 #pragma unroll
                 for (int i = 0; i < RPT; i += 4) {
-                    const float4 kk = kp[i >> 2], gg = gp[i >> 2];
-                    st[i] *= gg.x, st[i + 1] *= gg.y, st[i + 2] *= gg.z, st[i + 3] *= gg.w;
-                    d0 = fmaf(kk.x, st[i], d0), d1 = fmaf(kk.y, st[i + 1], d1), d2 = fmaf(kk.z, st[i + 2], d2), d3 = fmaf(kk.w, st[i + 3], d3);
+                    const float4 kk = kp[LANES * (i >> 2)], gg = gp[LANES * (i >> 2)];
+                    kr[i] = kk.x, kr[i + 1] = kk.y, kr[i + 2] = kk.z, kr[i + 3] = kk.w;
+                    const float gv[4] = {gg.x, gg.y, gg.z, gg.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+#pragma unroll
+                        for (int c = 0; c < CPT; ++c) {
+                            st[i + e][c] *= gv[e];
+                            dot[c] = fmaf(kr[i + e], st[i + e][c], dot[c]);
+                        }
                 }
-                float dot = (d0 + d1) + (d2 + d3);
 #pragma unroll
-                for (int w = LANES >> 1; w > 0; w >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, w);
-                const float u = beta * (v - dot);
+                for (int w = LANES >> 1; w > 0; w >>= 1)
+#pragma unroll
+                    for (int c = 0; c < CPT; ++c) dot[c] += __shfl_xor_sync(0xffffffffu, dot[c], w);
+                float u[CPT];
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) u[c] = beta * (v[c] - dot[c]);
 #pragma unroll
                 for (int i = 0; i < RPT; i += 4) {
-                    const float4 kk = kp[i >> 2], qq = qp[i >> 2];
-                    st[i] = fmaf(kk.x, u, st[i]), st[i + 1] = fmaf(kk.y, u, st[i + 1]), st[i + 2] = fmaf(kk.z, u, st[i + 2]), st[i + 3] = fmaf(kk.w, u, st[i + 3]);
-                    e0 = fmaf(qq.x, st[i], e0), e1 = fmaf(qq.y, st[i + 1], e1), e2 = fmaf(qq.z, st[i + 2], e2), e3 = fmaf(qq.w, st[i + 3], e3);
+                    const float4 qq = qp[LANES * (i >> 2)];
+                    const float qv[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+#pragma unroll
+                        for (int c = 0; c < CPT; ++c) {
+                            st[i + e][c] = fmaf(kr[i + e], u[c], st[i + e][c]);
+                            out[c] = fmaf(qv[e], st[i + e][c], out[c]);
+                        }
                 }
             } else {
                 const float gi = sb[tt * TS + NV * DP], gf = sb[tt * TS + NV * DP + 1];
                 const float m_new = fmaxf(gf + m, gi);
-                const float a = expf(gf + m - m_new), bv = expf(gi - m_new) * v;
+                const float a = expf(gf + m - m_new), b = expf(gi - m_new);
                 m = m_new;
+                float bv[CPT];
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) bv[c] = b * v[c];
 #pragma unroll
                 for (int i = 0; i < RPT; i += 4) {
-                    const float4 kk = kp[i >> 2], qq = qp[i >> 2];
-                    st[i] = fmaf(a, st[i], kk.x * bv), st[i + 1] = fmaf(a, st[i + 1], kk.y * bv), st[i + 2] = fmaf(a, st[i + 2], kk.z * bv), st[i + 3] = fmaf(a, st[i + 3], kk.w * bv);
-                    e0 = fmaf(qq.x, st[i], e0), e1 = fmaf(qq.y, st[i + 1], e1), e2 = fmaf(qq.z, st[i + 2], e2), e3 = fmaf(qq.w, st[i + 3], e3);
+                    const float4 kk = kp[LANES * (i >> 2)], qq = qp[LANES * (i >> 2)];
+                    const float kv[4] = {kk.x, kk.y, kk.z, kk.w}, qv[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+#pragma unroll
+                        for (int c = 0; c < CPT; ++c) {
+                            st[i + e][c] = fmaf(a, st[i + e][c], kv[e] * bv[c]);
+                            out[c] = fmaf(qv[e], st[i + e][c], out[c]);
+                        }
                 }
             }
-            float out = (e0 + e1) + (e2 + e3);
 #pragma unroll
-            for (int w = LANES >> 1; w > 0; w >>= 1) out += __shfl_xor_sync(0xffffffffu, out, w);
-            if (active && sub == 0) {
+            for (int w = LANES >> 1; w > 0; w >>= 1)
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) out[c] += __shfl_xor_sync(0xffffffffu, out[c], w);
+            if (sub == 0) {
                 const size_t tok = (size_t)(t0 + c0 + tt);
-                if (is_n) nq_out[tok * heads + h] = out, m_out[tok * heads + h] = m;
-                else o[(tok * heads + h) * vdim + col] = out;
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) {
+                    const int cc = col + c;
+                    if (MODE == 1 && cc == vdim) nq_out[tok * heads + h] = out[c], m_out[tok * heads + h] = m;
+                    else if (cc < vdim) o[(tok * heads + h) * vdim + cc] = out[c];
+                }
             }
         }
         __syncthreads();  // the stage is consumed: the fetch after next may overwrite it
     }
-    if (!active) return;
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
-        const int r = r0 + i;
-        if (r < dim) {
-            if (is_n) np[r] = st[i];
-            else Sp[(size_t)r * vdim + col] = st[i];
+        const int r = row_of(i);
+        if (r >= dim) continue;
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+            const int cc = col + c;
+            if (MODE == 1 && cc == vdim) np[r] = st[i][c];
+            else if (cc < vdim) Sp[(size_t)r * vdim + cc] = st[i][c];
         }
     }
-    if (is_n && sub == 0) m_state[(size_t)slot * heads + h] = m;
+    if (MODE == 1 && sub == 0 && col <= vdim && vdim < col + CPT) m_state[(size_t)slot * heads + h] = m;
 }
 
 // One warp per (token, head): out[t, h*vdim + j] = out_scale * y_j * rsqrt(mean_j y^2 + eps) * w[h * w_stride + j] * sigmoid(gate),
@@ -323,31 +373,35 @@ head_output_kernel(const float *__restrict__ o, const float *__restrict__ nq, co
     }
 }
 
-template <int DP, int LANES, int MODE>
+template <int DP, int LANES, int CPT, int MODE>
 static int launch_colrec_t(const float *rec, int rec_ld, int q_off, int k_off, int v_off, int a_off, int b_off, float *S, float *n_state,
                            float *m_state, float *o, float *nq, float *m_out, const int *seq_start, const int *seq_pos0, const int *seq_slot,
                            int n_seqs, int heads, int kv_heads, int dim, int vdim, cudaStream_t st) {
-    const int ncols = MODE == 1 ? vdim + 1 : vdim;
+    const int ncols = MODE == 1 ? vdim + 1 : vdim, groups = (ncols + CPT - 1) / CPT;
     // every CTA stages its head's key-side vectors for itself, so CTAs are as wide as the batch allows while about a hundred of them remain
-    const long long threads = (long long)ncols * LANES * heads * n_seqs;
+    const long long threads = (long long)groups * LANES * heads * n_seqs;
     int block = 256;
     while (block > 32 && block > LANES && threads / block < 100) block >>= 1;
     if (block < LANES) block = LANES;
-    const int cb = block / LANES;
+    const int cb = block / LANES * CPT;
     constexpr int NV = MODE == 0 ? 3 : 2;
     const size_t smem = ((size_t)2 * kRecTB * (NV * DP + 4) + (size_t)2 * kRecTB * cb) * sizeof(float);
-    auto kern = column_recurrence_kernel<DP, LANES, MODE>;
+    auto kern = column_recurrence_kernel<DP, LANES, CPT, MODE>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<dim3((ncols + cb - 1) / cb, heads, n_seqs), cb * LANES, smem, st>>>(rec, rec_ld, q_off, k_off, v_off, a_off, b_off, S, n_state, m_state, o, nq,
-                                                                             m_out, seq_start, seq_pos0, seq_slot, heads, kv_heads, dim, vdim);
+    kern<<<dim3((ncols + cb - 1) / cb, heads, n_seqs), block, smem, st>>>(rec, rec_ld, q_off, k_off, v_off, a_off, b_off, S, n_state, m_state, o, nq, m_out,
+                                                                        seq_start, seq_pos0, seq_slot, heads, kv_heads, dim, vdim);
     return cuda_status("column_recurrence launch");
 }
 
-// how many lanes share a column: as many as it takes to give the device about two warps per SM, within what the padded key size allows
-// (at least 4 rows per lane for the 16-byte shared-memory reads, at most 128 for the registers)
-static int pick_lanes(int dp, long long columns) {
-    int lanes = dp > 128 ? dp / 128 : 1;
-    while (lanes < 16 && dp / (2 * lanes) >= 4 && columns * lanes < 148LL * 2 * 32) lanes *= 2;
+// how many lanes share a column group: at least what keeps a thread's state tile within its registers (rows per lane <= max_rows), then as
+// many as it takes to give the device about two warps per SM, down to four rows per lane (one 16-byte piece of a staged vector)
+static int pick_lanes(int dp, int max_rows, long long groups) {
+    int lanes = dp > max_rows ? dp / max_rows : 1;
+    if (const char *e = getenv("B200_RECURRENCE_LANES")) {  // measurement aid: a fixed lane count (a power of two within the limits)
+        const int want = atoi(e);
+        if (want >= lanes && want <= 32 && (want & (want - 1)) == 0 && dp / want >= 4) return want;
+    }
+    while (lanes < 16 && dp / (2 * lanes) >= 4 && groups * lanes < 148LL * 2 * 32) lanes *= 2;
     return lanes;
 }
 
@@ -361,16 +415,20 @@ static int launch_colrec(const float *rec, int rec_ld, int q_off, int k_off, int
         return B200_ERR_UNSUPPORTED;
     }
     const int dp = dim <= 16 ? 16 : (dim <= 32 ? 32 : (dim <= 64 ? 64 : (dim <= 128 ? 128 : (dim <= 256 ? 256 : 512))));
-    const int lanes = pick_lanes(dp, (long long)n_seqs * heads * (vdim + MODE));
-#define B200_COLREC(D, L)  \
-    if (dp == D && lanes == L) \
-        return launch_colrec_t<D, L, MODE>(rec, rec_ld, q_off, k_off, v_off, a_off, b_off, S, n_state, m_state, o, nq, m_out, seq_start, seq_pos0, seq_slot, n_seqs, heads, kv_heads, dim, vdim, st)
-    B200_COLREC(16, 1); B200_COLREC(16, 2); B200_COLREC(16, 4);
-    B200_COLREC(32, 1); B200_COLREC(32, 2); B200_COLREC(32, 4); B200_COLREC(32, 8);
-    B200_COLREC(64, 1); B200_COLREC(64, 2); B200_COLREC(64, 4); B200_COLREC(64, 8); B200_COLREC(64, 16);
-    B200_COLREC(128, 1); B200_COLREC(128, 2); B200_COLREC(128, 4); B200_COLREC(128, 8); B200_COLREC(128, 16);
-    B200_COLREC(256, 2); B200_COLREC(256, 4); B200_COLREC(256, 8); B200_COLREC(256, 16);
-    B200_COLREC(512, 4); B200_COLREC(512, 8); B200_COLREC(512, 16);
+    const int ncols = vdim + MODE;
+    // one column per thread: measured against tiles of four columns (fewer shared-memory reads per multiply-add, but a quarter of the threads),
+    // the single column won at every batch shape but one: the token loop is bound by its chain of dependent steps, not by its loads
+    constexpr int cpt = 1;
+    const int lanes = pick_lanes(dp, 64, (long long)n_seqs * heads * ncols);
+#define B200_COLREC(D, L, C)  \
+    if (dp == D && lanes == L && cpt == C) \
+        return launch_colrec_t<D, L, C, MODE>(rec, rec_ld, q_off, k_off, v_off, a_off, b_off, S, n_state, m_state, o, nq, m_out, seq_start, seq_pos0, seq_slot, n_seqs, heads, kv_heads, dim, vdim, st)
+    B200_COLREC(16, 1, 1); B200_COLREC(16, 2, 1); B200_COLREC(16, 4, 1);
+    B200_COLREC(32, 1, 1); B200_COLREC(32, 2, 1); B200_COLREC(32, 4, 1); B200_COLREC(32, 8, 1);
+    B200_COLREC(64, 1, 1); B200_COLREC(64, 2, 1); B200_COLREC(64, 4, 1); B200_COLREC(64, 8, 1); B200_COLREC(64, 16, 1);
+    B200_COLREC(128, 2, 1); B200_COLREC(128, 4, 1); B200_COLREC(128, 8, 1); B200_COLREC(128, 16, 1); B200_COLREC(128, 32, 1);
+    B200_COLREC(256, 4, 1); B200_COLREC(256, 8, 1); B200_COLREC(256, 16, 1); B200_COLREC(256, 32, 1);
+    B200_COLREC(512, 8, 1); B200_COLREC(512, 16, 1); B200_COLREC(512, 32, 1);
 #undef B200_COLREC
     set_error("column recurrence: no kernel for key size %d with %d lanes", dim, lanes);
     return B200_ERR_UNSUPPORTED;
