@@ -54,13 +54,17 @@ delta_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__r
     const int nqk = kv_heads * dim, nv = heads * vdim, channels = 2 * nqk + nv;
     float *cv = sh;
     const float *cst = conv_state + (size_t)slot * (taps - 1) * channels;
+    // every tap reads both places it could come from at an index that always exists and keeps the one that is meant: no branch stands
+    // between the loads, so the taps' (and, unrolled, four channels') loads are in flight together
+    const int keep = taps > 1 ? taps - 1 : 1;
+#pragma unroll 4
     for (int c = threadIdx.x; c < channels; c += blockDim.x) {
         float acc = 0.0f;
         for (int j = 0; j < taps; ++j) {
             const int back = taps - 1 - j, pp = pos - back;  // the input `back` tokens ago
-            float x = 0.0f;
-            if (pp >= pos0) x = Elem<T>::to_f(proj[(size_t)(t - back) * ld + col0 + c]);
-            else if (pp >= 0) x = cst[(size_t)(pp - (pos0 - (taps - 1))) * channels + c];
+            const float xp = Elem<T>::to_f(proj[(size_t)max(t - back, 0) * ld + col0 + c]);
+            const float xs = cst[(size_t)min(max(pp - (pos0 - (taps - 1)), 0), keep - 1) * channels + c];
+            const float x = pp >= pos0 ? xp : (pp >= 0 ? xs : 0.0f);
             acc = fmaf(conv_w[(size_t)c * taps + j], x, acc);
         }
         cv[c] = acc * sigmoid_r(acc);
@@ -108,13 +112,13 @@ conv_state_update_kernel(const T *__restrict__ proj, int ld, int col0, float *__
     const int s = blockIdx.x, t0 = seq_start[s], len = seq_start[s + 1] - t0, pos0 = seq_pos0[s], keep = taps - 1;
     if (len <= 0) return;
     float *cst = conv_state + (size_t)seq_slot[s] * keep * channels;
+#pragma unroll 2
     for (int c = threadIdx.x; c < channels; c += blockDim.x) {
         for (int r = 0; r < keep; ++r) {  // new row r holds the input at position pos0 + len - keep + r; ascending r reads rows >= r only
             const int i = len - keep + r;  // index into the portion
-            float x = 0.0f;
-            if (i >= 0) x = Elem<T>::to_f(proj[(size_t)(t0 + i) * ld + col0 + c]);
-            else if (pos0 + i >= 0) x = cst[(size_t)(r + len) * channels + c];
-            cst[(size_t)r * channels + c] = x;
+            const float xp = Elem<T>::to_f(proj[(size_t)(t0 + max(i, 0)) * ld + col0 + c]);
+            const float xs = cst[(size_t)min(r + len, keep - 1) * channels + c];
+            cst[(size_t)r * channels + c] = i >= 0 ? xp : (pos0 + i >= 0 ? xs : 0.0f);
         }
     }
 }
@@ -454,7 +458,8 @@ int launch_delta_prep(int dtype, const void *proj, int ld, int col0, const float
     float *zs[2] = {za, zg};
     const int ns[2] = {heads * dim, heads * vdim}, ks[2] = {rank, gate_rank};
     for (int i = 0; i < 2; ++i) {
-        rc = launch_dense_f32out(dtype, xs[i], ws[i], zs[i], tokens, ns[i], ks[i], st);
+        // (few tokens are a single 64-row tile on the tensor-core kernel -- few CTAs, each walking all of K: they take the fp32 kernel too)
+        rc = tokens >= 64 ? launch_dense_f32out(dtype, xs[i], ws[i], zs[i], tokens, ns[i], ks[i], st) : B200_ERR_UNSUPPORTED;
         if (rc == B200_ERR_UNSUPPORTED) rc = launch_proj_f32(dtype, xs[i], ks[i], dtype, ws[i], nullptr, zs[i], ns[i], tokens, ns[i], ks[i], st);
         if (rc != B200_OK) return rc;
     }
