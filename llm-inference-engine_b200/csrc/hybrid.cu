@@ -1067,7 +1067,7 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
                                   l.gate_rank, m->mix2, m->f32a, m->f32b, m->rec, d_seq, d_pos, d_pos0, d_slot, NT, l.heads, l.kv_heads, l.dim, l.vdim, st));
             RUN(launch_conv_state_update(dt, m->proj, n_in, col, conv_state, l.conv, 2 * l.kv_heads * l.dim + l.heads * l.vdim, d_start, d_pos0, d_slot, S, st));
             RUN(launch_delta_recurrent(m->rec, (float *)(m->state_pool + mp.state_off), m->f32b, d_start, d_pos0, d_slot, S, l.heads, l.kv_heads, l.dim,
-                                       l.vdim, st));
+                                       l.vdim, st, gla_kinds == kGlaOneToken));
             RUN(launch_head_output(dt, m->f32b, nullptr, nullptr, l.out_norm, 0, c.norm_eps, m->rec + lay.gate, lay.ld, nullptr, 0, out, n_cat, out_scale, NT,
                                    l.heads, l.vdim, st));
         } else {
@@ -1075,7 +1075,7 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
             float *nq = m->f32c, *mo = m->f32c + (size_t)NT * l.heads;
             RUN(launch_mlstm_prep(dt, m->proj, n_in, col, l.b_in, l.gate_cap, m->rec, NT, l.heads, l.dim, l.vdim, st));
             RUN(launch_mlstm_recurrent(m->rec, (float *)(m->state_pool + mp.state_off), (float *)(m->state_pool + mp.aux_off),
-                                       (float *)(m->state_pool + mp.aux2_off), m->f32b, nq, mo, d_start, d_pos0, d_slot, S, l.heads, l.dim, l.vdim, st));
+                                       (float *)(m->state_pool + mp.aux2_off), m->f32b, nq, mo, d_start, d_pos0, d_slot, S, l.heads, l.dim, l.vdim, st, gla_kinds == kGlaOneToken));
             RUN(launch_head_output(dt, m->f32b, nq, mo, l.out_norm, l.vdim, c.norm_eps, nullptr, 0, gate, n_in, out, n_cat, out_scale, NT, l.heads, l.vdim, st));
         }
         return B200_OK;

@@ -62,12 +62,13 @@ int launch_delta_prep(int dtype, const void *proj, int ld, int col0, const float
                       int kv_heads, int dim, int vdim, cudaStream_t st);
 int launch_conv_state_update(int dtype, const void *proj, int ld, int col0, float *conv_state, int taps, int channels, const int *seq_start,
                              const int *seq_pos0, const int *seq_slot, int n_seqs, cudaStream_t st);
+// one_token: the host knows that every portion of the batch is a single token (a decode batch)
 int launch_delta_recurrent(const float *rec, float *S, float *o, const int *seq_start, const int *seq_pos0, const int *seq_slot, int n_seqs,
-                           int heads, int kv_heads, int dim, int vdim, cudaStream_t st);
+                           int heads, int kv_heads, int dim, int vdim, cudaStream_t st, int one_token = 0);
 int launch_mlstm_prep(int dtype, const void *proj, int ld, int col0, const float *b_in, float cap, float *rec, int tokens, int heads, int dim,
                       int vdim, cudaStream_t st);
 int launch_mlstm_recurrent(const float *rec, float *S, float *n_state, float *m_state, float *o, float *nq, float *m_out, const int *seq_start,
-                           const int *seq_pos0, const int *seq_slot, int n_seqs, int heads, int dim, int vdim, cudaStream_t st);
+                           const int *seq_pos0, const int *seq_slot, int n_seqs, int heads, int dim, int vdim, cudaStream_t st, int one_token = 0);
 // out[t, h*vdim + j] = out_scale * y * rsqrt(mean_j y^2 + eps) * w[h*w_stride + j] * sigmoid(gate); y = o, or o / (max(|nq|, exp(-m)) + 1e-6)
 int launch_head_output(int dtype, const float *o, const float *nq, const float *m_in, const float *w, int w_stride, float eps,
                        const float *gate_f, int gate_f_ld, const void *gate_t, int gate_t_ld, void *out, int out_ld, float out_scale, int tokens,

@@ -103,17 +103,16 @@ delta_finish_kernel(const float *__restrict__ za, const float *__restrict__ zg, 
     for (int c = threadIdx.x; c < nv; c += blockDim.x) out[lay.gate + c] = zg[(size_t)t * nv + c];
 }
 
-// After the convolutions have read it: the state's rows move up by the portion's length and its last inputs come in.  One CTA per
-// sequence; a thread owns whole channels, so it reads what it overwrites before it does.
+// After the convolutions have read it: the state's rows move up by the portion's length and its last inputs come in.  grid (channel
+// blocks, sequences); a thread owns a whole channel, so it reads what it overwrites before it does.
 template <typename T>
 __global__ void __launch_bounds__(256)
 conv_state_update_kernel(const T *__restrict__ proj, int ld, int col0, float *__restrict__ conv_state, int taps, int channels,
                          const int *__restrict__ seq_start, const int *__restrict__ seq_pos0, const int *__restrict__ seq_slot) {
-    const int s = blockIdx.x, t0 = seq_start[s], len = seq_start[s + 1] - t0, pos0 = seq_pos0[s], keep = taps - 1;
+    const int s = blockIdx.y, t0 = seq_start[s], len = seq_start[s + 1] - t0, pos0 = seq_pos0[s], keep = taps - 1;
     if (len <= 0) return;
     float *cst = conv_state + (size_t)seq_slot[s] * keep * channels;
-#pragma unroll 2
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < channels; c += gridDim.x * blockDim.x) {
         for (int r = 0; r < keep; ++r) {  // new row r holds the input at position pos0 + len - keep + r; ascending r reads rows >= r only
             const int i = len - keep + r;  // index into the portion
             const float xp = Elem<T>::to_f(proj[(size_t)(t0 + max(i, 0)) * ld + col0 + c]);
@@ -380,12 +379,15 @@ head_output_kernel(const float *__restrict__ o, const float *__restrict__ nq, co
 template <int DP, int LANES, int CPT, int MODE>
 static int launch_colrec_t(const float *rec, int rec_ld, int q_off, int k_off, int v_off, int a_off, int b_off, float *S, float *n_state,
                            float *m_state, float *o, float *nq, float *m_out, const int *seq_start, const int *seq_pos0, const int *seq_slot,
-                           int n_seqs, int heads, int kv_heads, int dim, int vdim, cudaStream_t st) {
+                           int n_seqs, int heads, int kv_heads, int dim, int vdim, int one_token, cudaStream_t st) {
     const int ncols = MODE == 1 ? vdim + 1 : vdim, groups = (ncols + CPT - 1) / CPT;
     // every CTA stages its head's key-side vectors for itself, so CTAs are as wide as the batch allows while about a hundred of them remain
     const long long threads = (long long)groups * LANES * heads * n_seqs;
     int block = 256;
     while (block > 32 && block > LANES && threads / block < 100) block >>= 1;
+    // a batch of one-token portions stages next to nothing: small CTAs leave fewer idle threads behind the last column (the normaliser's
+    // column makes the column count odd) and fill the SMs evenly
+    if (one_token && block > 64) block = 64;
     if (block < LANES) block = LANES;
     const int cb = block / LANES * CPT;
     constexpr int NV = MODE == 0 ? 3 : 2;
@@ -412,7 +414,7 @@ static int pick_lanes(int dp, int max_rows, long long groups) {
 template <int MODE>
 static int launch_colrec(const float *rec, int rec_ld, int q_off, int k_off, int v_off, int a_off, int b_off, float *S, float *n_state,
                          float *m_state, float *o, float *nq, float *m_out, const int *seq_start, const int *seq_pos0, const int *seq_slot,
-                         int n_seqs, int heads, int kv_heads, int dim, int vdim, cudaStream_t st) {
+                         int n_seqs, int heads, int kv_heads, int dim, int vdim, int one_token, cudaStream_t st) {
     if (n_seqs == 0) return B200_OK;
     if (dim > 512) {
         set_error("column recurrence: key size %d above 512", dim);
@@ -426,7 +428,7 @@ static int launch_colrec(const float *rec, int rec_ld, int q_off, int k_off, int
     const int lanes = pick_lanes(dp, 64, (long long)n_seqs * heads * ncols);
 #define B200_COLREC(D, L, C)  \
     if (dp == D && lanes == L && cpt == C) \
-        return launch_colrec_t<D, L, C, MODE>(rec, rec_ld, q_off, k_off, v_off, a_off, b_off, S, n_state, m_state, o, nq, m_out, seq_start, seq_pos0, seq_slot, n_seqs, heads, kv_heads, dim, vdim, st)
+        return launch_colrec_t<D, L, C, MODE>(rec, rec_ld, q_off, k_off, v_off, a_off, b_off, S, n_state, m_state, o, nq, m_out, seq_start, seq_pos0, seq_slot, n_seqs, heads, kv_heads, dim, vdim, one_token, st)
     B200_COLREC(16, 1, 1); B200_COLREC(16, 2, 1); B200_COLREC(16, 4, 1);
     B200_COLREC(32, 1, 1); B200_COLREC(32, 2, 1); B200_COLREC(32, 4, 1); B200_COLREC(32, 8, 1);
     B200_COLREC(64, 1, 1); B200_COLREC(64, 2, 1); B200_COLREC(64, 4, 1); B200_COLREC(64, 8, 1); B200_COLREC(64, 16, 1);
@@ -471,16 +473,16 @@ int launch_conv_state_update(int dtype, const void *proj, int ld, int col0, floa
                              const int *seq_pos0, const int *seq_slot, int n_seqs, cudaStream_t st) {
     if (n_seqs == 0 || taps <= 1) return B200_OK;
     B200_DISPATCH_DTYPE(dtype, {
-        conv_state_update_kernel<T><<<n_seqs, 256, 0, st>>>((const T *)proj, ld, col0, conv_state, taps, channels, seq_start, seq_pos0, seq_slot);
+        conv_state_update_kernel<T><<<dim3((channels + 255) / 256, n_seqs), 256, 0, st>>>((const T *)proj, ld, col0, conv_state, taps, channels, seq_start, seq_pos0, seq_slot);
     });
     return cuda_status("conv_state_update launch");
 }
 
 int launch_delta_recurrent(const float *rec, float *S, float *o, const int *seq_start, const int *seq_pos0, const int *seq_slot, int n_seqs,
-                           int heads, int kv_heads, int dim, int vdim, cudaStream_t st) {
+                           int heads, int kv_heads, int dim, int vdim, cudaStream_t st, int one_token) {
     const DeltaRow lay = delta_row(heads, kv_heads, dim, vdim);
     return launch_colrec<0>(rec, lay.ld, lay.q, lay.k, lay.v, lay.decay, lay.beta, S, nullptr, nullptr, o, nullptr, nullptr, seq_start, seq_pos0,
-                            seq_slot, n_seqs, heads, kv_heads, dim, vdim, st);
+                            seq_slot, n_seqs, heads, kv_heads, dim, vdim, one_token, st);
 }
 
 int launch_mlstm_prep(int dtype, const void *proj, int ld, int col0, const float *b_in, float cap, float *rec, int tokens, int heads, int dim,
@@ -492,10 +494,10 @@ int launch_mlstm_prep(int dtype, const void *proj, int ld, int col0, const float
 }
 
 int launch_mlstm_recurrent(const float *rec, float *S, float *n_state, float *m_state, float *o, float *nq, float *m_out, const int *seq_start,
-                           const int *seq_pos0, const int *seq_slot, int n_seqs, int heads, int dim, int vdim, cudaStream_t st) {
+                           const int *seq_pos0, const int *seq_slot, int n_seqs, int heads, int dim, int vdim, cudaStream_t st, int one_token) {
     const MlstmRow lay = mlstm_row(heads, dim, vdim);
     return launch_colrec<1>(rec, lay.ld, lay.q, lay.k, lay.v, lay.gi, lay.gf, S, n_state, m_state, o, nq, m_out, seq_start, seq_pos0, seq_slot,
-                            n_seqs, heads, heads, dim, vdim, st);
+                            n_seqs, heads, heads, dim, vdim, one_token, st);
 }
 
 int launch_head_output(int dtype, const float *o, const float *nq, const float *m_in, const float *w, int w_stride, float eps,
@@ -520,7 +522,7 @@ int b200_delta_rule_recurrent(const float *rec, float *state, float *o, const in
                               int n_seqs, int heads, int kv_heads, int dim, int vdim, b200_stream_t stream) {
     B200_REQUIRE(rec && state && o && seq_start && seq_pos0 && seq_slot, "delta_rule_recurrent: null pointer");
     B200_REQUIRE(n_seqs >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0, "delta_rule_recurrent: bad shape");
-    return launch_delta_recurrent(rec, state, o, seq_start, seq_pos0, seq_slot, n_seqs, heads, kv_heads, dim, vdim, as_stream(stream));
+    return launch_delta_recurrent(rec, state, o, seq_start, seq_pos0, seq_slot, n_seqs, heads, kv_heads, dim, vdim, as_stream(stream), 0);
 }
 
 int b200_mlstm_recurrent(const float *rec, float *state, float *n_state, float *m_state, float *o, float *nq, float *m_out,
@@ -529,6 +531,6 @@ int b200_mlstm_recurrent(const float *rec, float *state, float *n_state, float *
     B200_REQUIRE(rec && state && n_state && m_state && o && nq && m_out && seq_start && seq_pos0 && seq_slot, "mlstm_recurrent: null pointer");
     B200_REQUIRE(n_seqs >= 0 && heads > 0 && dim > 0 && vdim > 0, "mlstm_recurrent: bad shape");
     return launch_mlstm_recurrent(rec, state, n_state, m_state, o, nq, m_out, seq_start, seq_pos0, seq_slot, n_seqs, heads, dim, vdim,
-                                  as_stream(stream));
+                                  as_stream(stream), 0);
 }
 }
