@@ -362,6 +362,40 @@ proj_f32_small_kernel(const TX *__restrict__ x, int ldx, const TW *__restrict__ 
     if (lane == 0) y[(size_t)mrow * ldy + n] = v + (bias ? bias[n] : 0.0f);
 }
 
+// A decode batch against a wide matrix (M <= 16 rows, any N): one warp per output column walks K in 16-byte pieces; a weight piece is read
+// once for all rows, the rows' pieces come from L1 (M * K elements, the same for every warp).  x and w of the same 16-bit type T.
+template <typename T, int PM>
+__global__ void __launch_bounds__(256)
+proj_f32_rows_kernel(const T *__restrict__ x, int ldx, const T *__restrict__ w, const float *__restrict__ bias, float *__restrict__ y, int ldy, int M,
+                     int N, int K) {
+    constexpr int V = Elem<T>::kVec;
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    float acc[PM];
+#pragma unroll
+    for (int i = 0; i < PM; ++i) acc[i] = 0.0f;
+    const T *wr = w + (size_t)n * K;
+#pragma unroll 2
+    for (int k = lane * V; k < K; k += 32 * V) {
+        float wv[V];
+        unpack16<T>(ld_stream_v4(wr + k), wv);
+#pragma unroll
+        for (int i = 0; i < PM; ++i) {
+            if (i < M) {
+                float xv[V];
+                unpack16<T>(ld_v4(x + (size_t)i * ldx + k), xv);
+#pragma unroll
+                for (int e = 0; e < V; ++e) acc[i] = fmaf(xv[e], wv[e], acc[i]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < PM; ++i) {
+        const float v = warp_sum(acc[i]);
+        if (lane == 0 && i < M) y[(size_t)i * ldy + n] = v + (bias ? bias[n] : 0.0f);
+    }
+}
+
 template <typename TX, typename TW, int PM>
 static void launch_proj_f32_t(const void *x, int ldx, const void *w, const float *bias, float *y, int ldy, int M, int N, int K, cudaStream_t st) {
     const size_t smem = (size_t)PM * K * sizeof(float);
@@ -383,6 +417,17 @@ int launch_proj_f32(int x_dtype, const void *x, int ldx, int w_dtype, const void
             else proj_f32_small_kernel<T, T><<<grid, 256, 0, st>>>((const T *)x, ldx, (const T *)w, bias, y, ldy, M, N, K);
         });
         return cuda_status("proj_f32 (small) launch");
+    }
+    if (M <= 16 && x_dtype == w_dtype && w_dtype != B200_F32 && K % 8 == 0 && ldx % 8 == 0 && K >= 512 && aligned16(x) && aligned16(w)) {
+        const int grid = (N + 7) / 8;
+        if (w_dtype == B200_BF16) {
+            if (M <= 8) proj_f32_rows_kernel<__nv_bfloat16, 8><<<grid, 256, 0, st>>>((const __nv_bfloat16 *)x, ldx, (const __nv_bfloat16 *)w, bias, y, ldy, M, N, K);
+            else proj_f32_rows_kernel<__nv_bfloat16, 16><<<grid, 256, 0, st>>>((const __nv_bfloat16 *)x, ldx, (const __nv_bfloat16 *)w, bias, y, ldy, M, N, K);
+        } else {
+            if (M <= 8) proj_f32_rows_kernel<__half, 8><<<grid, 256, 0, st>>>((const __half *)x, ldx, (const __half *)w, bias, y, ldy, M, N, K);
+            else proj_f32_rows_kernel<__half, 16><<<grid, 256, 0, st>>>((const __half *)x, ldx, (const __half *)w, bias, y, ldy, M, N, K);
+        }
+        return cuda_status("proj_f32 (rows) launch");
     }
     if ((size_t)4 * K * sizeof(float) > 200 * 1024) {
         set_error("proj_f32: K = %d does not fit the shared-memory activation tile", K);
@@ -1086,7 +1131,8 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
         const LayerPlan &lp = m->plan[run];
         const b200_hybrid_layer_t &l = m->layers[lp.layer];
         if (lp.entry >= 0) {  // x <- w_entry [x ; x0] + step[pass], fp32 out; then this layer's norm
-            rc = launch_dense_f32out(dt, m->xc, m->w_entry, m->xn, NT, width, 2 * width, st);
+            // (a decode batch is a single row tile on the tensor-core kernel -- N / 128 CTAs, each walking all of K: it takes the row kernel)
+            rc = NT > 16 ? launch_dense_f32out(dt, m->xc, m->w_entry, m->xn, NT, width, 2 * width, st) : B200_ERR_UNSUPPORTED;
             if (rc == B200_ERR_UNSUPPORTED) rc = launch_proj_f32(dt, m->xc, 2 * width, dt, m->w_entry, nullptr, m->xn, width, NT, width, 2 * width, st);
             if (rc != B200_OK) return rc;
             RUN(ln_residual(nullptr, m->xn, m->loop_step + (size_t)lp.entry * width, l.pre1, m->h, width, nullptr));

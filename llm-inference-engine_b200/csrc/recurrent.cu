@@ -44,7 +44,7 @@ MlstmRow mlstm_row(int heads, int dim, int vdim) {
 // Writes q, k (unit vectors), v and the step of the token's fp32 row, and the two low-rank inputs as dense rows lr_a [tokens, rank],
 // lr_g [tokens, gate_rank] for the products that follow.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 delta_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__restrict__ conv_w, int taps, const float *__restrict__ conv_state,
                   int rank, int gate_rank, T *__restrict__ lr_a, T *__restrict__ lr_g, float *__restrict__ rec, DeltaRow lay,
                   const int *__restrict__ tok_seq, const int *__restrict__ tok_pos, const int *__restrict__ seq_pos0,
@@ -450,7 +450,8 @@ int launch_delta_prep(int dtype, const void *proj, int ld, int col0, const float
     void *lr_a = lr, *lr_g = (char *)lr + (((size_t)tokens * rank * es + 255) & ~(size_t)255);
     B200_DISPATCH_DTYPE(dtype, {
         if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        delta_prep_kernel<T><<<tokens, 256, smem, st>>>((const T *)proj, ld, col0, conv_w, taps, conv_state, rank, gate_rank, (T *)lr_a, (T *)lr_g, rec, lay,
+        // few tokens: few CTAs, so each gets more threads (a thread's channels are a chain of load latencies)
+        delta_prep_kernel<T><<<tokens, tokens <= 64 ? 1024 : 256, smem, st>>>((const T *)proj, ld, col0, conv_w, taps, conv_state, rank, gate_rank, (T *)lr_a, (T *)lr_g, rec, lay,
                                                        tok_seq, tok_pos, seq_pos0, seq_slot, heads, kv_heads, dim, vdim);
     });
     int rc = cuda_status("delta_prep launch");
