@@ -345,6 +345,18 @@ def test_tensor_core_attention_against_the_oracle_and_against_single_tokens(dim,
     assert ref.rel_err(tiles, want) < 4e-2 and ref.rel_err(single, want) < 4e-2 and ref.rel_err(tiles, single) < 3e-2
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rank", [8, 24])
+def test_low_rank_halves_of_the_delta_rule_on_both_product_kernels(rank, dtype):
+    """Portions of 64 tokens and more form the decay's and the gate's second halves on the tensor cores (inner sizes that are multiples
+    of 8), shorter ones and other inner sizes on the fp32 kernel; the gate's inner size is rank + 1."""
+    config = ref.make_config([ref.pair_layer(r_heads=4, r_kv_heads=2, r_dim=16, r_vdim=16, mlp=ref.dense())], width=64)
+    W, packed = ref.make_weights(config, seed=rank, low_rank=rank)
+    reqs = {"a": tokens_of(config, 150, 24)}
+    got = replay(session(config, packed, dtype=dtype), reqs, [[("a", 100)], [("a", 3)], [("a", 47)]])
+    check_all(got, config, W, reqs, 5e-5 if dtype == "float32" else 6e-2)
+
+
 # ------------------------------------------------------------------ state that is carried, and state that must not be
 def test_a_slot_used_again_starts_from_nothing():
     """The second request takes the slot and the pages of the first: neither its matrix states, nor its running maximum, nor the
