@@ -375,7 +375,7 @@ proj_f32_rows_kernel(const T *__restrict__ x, int ldx, const T *__restrict__ w, 
 #pragma unroll
     for (int i = 0; i < PM; ++i) acc[i] = 0.0f;
     const T *wr = w + (size_t)n * K;
-#pragma unroll 2
+#pragma unroll 4
     for (int k = lane * V; k < K; k += 32 * V) {
         float wv[V];
         unpack16<T>(ld_stream_v4(wr + k), wv);
