@@ -438,7 +438,12 @@ typedef enum {
                                     logarithmic distance penalty, weights by softmax or by an un-normalised sigmoid, output gate      */
     B200_MIXER_DELTA = 5,        /* gated delta rule: short causal convolutions, unit q/k, a decay per head and key channel, fp32
                                     matrix state per head that is corrected towards the value before it is read                      */
-    B200_MIXER_MLSTM = 6         /* matrix memory with exponential input gate, sigmoid forget gate and a running maximum (mLSTM)     */
+    B200_MIXER_MLSTM = 6,        /* matrix memory with exponential input gate, sigmoid forget gate and a running maximum (mLSTM)     */
+    B200_MIXER_SSD = 7,          /* state-space mixer with a scalar decay per head and token (Mamba-2): short causal convolution on x, B
+                                    and C, a softplus step size per head, fp32 matrix state [state, vdim] per head, a skip term, the
+                                    result gated by silu(z) and RMS-normed in equal groups                                           */
+    B200_MIXER_LINEAR = 8        /* linear attention with ONE constant decay per head: silu on q, k and v, fp32 matrix state per head,
+                                    RMS norm over the concatenated heads, sigmoid output gate                                        */
 } b200_mixer_kind_t;
 typedef enum { B200_ATTN_SOFTMAX = 0, B200_ATTN_SIGMOID = 1 } b200_attn_weight_t;
 typedef enum { B200_MLP_NONE = 0, B200_MLP_MOE = 1, B200_MLP_DENSE = 2 } b200_mlp_kind_t;
@@ -446,10 +451,17 @@ typedef enum { B200_ACT_RELU2 = 0, B200_ACT_SILU = 1, B200_ACT_GELU_TANH = 2, B2
 typedef enum {
     B200_NORM_RMS_POST = 0,      /* x += rmsnorm(sublayer(x)) * g                                                                     */
     B200_NORM_DYT_PRE_POST = 1,  /* x += ls * dyt_b(sublayer(dyt_a(x))), dyt(v) = tanh(alpha v) * w + b: no mean, no variance         */
-    B200_NORM_LN_PARALLEL = 2    /* y = layernorm(x) (weight and bias, packed [w | b] in pre1);  x += mixer(y) + ff(y): ONE norm, both
+    B200_NORM_LN_PARALLEL = 2,   /* y = layernorm(x) (weight and bias, packed [w | b] in pre1);  x += mixer(y) + ff(y): ONE norm, both
                                     sublayers read it.  Their input projections are one matrix (w_in: mixer rows, side mixer rows,
                                     then the feed-forward's gate rows and up rows) and so are their output projections (w_out
                                     [width, mixer columns | side mixer columns | expert_ff]); w_up / w_down stay NULL                 */
+    B200_NORM_LN_PRE = 3         /* pre-norm with two layer norms (pre1 / pre2, packed [w | b]): x += mixer(ln1(x)); x += ff(ln2(x)).
+                                    With residual streams (config streams >= 1 and hc1 / hc2 set) a sublayer reads u = sum_s in[s] x_s
+                                    and all streams are rewritten at once: x_t <- sum_s mix[s][t] x_s + out[t] * sublayer(ln(u)); the
+                                    model's result is the sum of the streams.  w_in holds the mixer's rows, then the side mixer's;
+                                    every mixer has an output projection of its own (w_out; side->w_out); with branch_norm set, the
+                                    mixer sublayer's result is mix_scale * rmsnorm(mixer) * branch_norm + side_scale * rmsnorm(side) *
+                                    side->branch_norm.  Feed-forward: DENSE, gated (w_up [2*expert_ff, width]: gate rows, then up rows) */
 } b200_norm_kind_t;
 typedef enum {
     B200_ROUTE_SIGMOID = 0,      /* scores = sigmoid(logits), the chosen scores are the weights, applied to the expert's INPUT        */
@@ -471,6 +483,8 @@ typedef struct {
     int loop_start, loop_stop, loop_times; /* loop_times > 0: layers [loop_start, loop_stop) run loop_times times in a row with the same
                            weights, every pass with a cache and state of its own (b200_hybrid_set_loop gives the entry step's weights);
                            0: every layer runs once                                                                                  */
+    float logit_scale;  /* logits <- logits * logit_scale (before the soft cap); 0 reads as 1                                         */
+    int streams;        /* LN_PRE layers: residual streams (1 .. 8); 0 reads as 1                                                     */
 } b200_hybrid_config_t;
 
 typedef struct b200_hybrid_layer_s {
@@ -539,6 +553,26 @@ typedef struct b200_hybrid_layer_s {
     /* ---- a second mixer beside the first: both read the same input, result = mix_scale * mixer + side_scale * side mixer */
     const struct b200_hybrid_layer_s *side; /* only its mixer fields are read (LN_PARALLEL layers); NULL: none                        */
     float mix_scale, side_scale;  /* read only when there is a second mixer                                                           */
+    /* ---- more options of ATTN_SCORED */
+    int rot_half;                 /* 1: the rotating pairs are (i, i + rot_dims/2) instead of (2i, 2i+1)                              */
+    float rot_factor, rot_low, rot_high, rot_original; /* rot_factor > 0: the frequency f of a pair with wavelength l = 2 pi / f stays
+                                     where l < original / high, becomes f / factor where l > original / low, and between the two
+                                     (1 - s) f / factor + s f with s = (original / l - low) / (high - low)                            */
+    int v_norm;                   /* 1: every value head is divided by its root mean square (norm_eps) before it is cached            */
+    float softcap;                /* > 0: score <- softcap * tanh(score / softcap), after the scale                                   */
+    /* ---- DELTA with decay_rank == 0: w_in rows q, k, v, step (heads), decay-in (heads), gate (heads*vdim): ONE decay per head,
+     *      exp(-exp(a_log[h]) * softplus(decay-in[h] + decay_bias[h])), and a full-rank output gate */
+    int gate_act;                 /* DELTA: 0: the read-out is multiplied by sigmoid(gate), 1: by silu(gate)                          */
+    /* ---- SSD: heads, vdim, dim = state size, kv_heads = groups of B and C; w_in rows z, x (heads*vdim each), B, C (kv_heads*dim each), dt
+     *      (heads); conv / conv_w / conv_b over the channels x | B | C; decay_bias [heads] = the step size's bias; a_log [heads];
+     *      out_norm [heads*vdim].    LINEAR: w_in rows q, k (heads*dim each), v, gate (heads*vdim each); out_norm [heads*vdim] */
+    const float *conv_b;          /* SSD: [channels] bias of the convolution, or NULL                                                 */
+    const float *skip;            /* SSD: [heads]: out += skip[h] * x                                                                 */
+    int norm_groups;              /* SSD: the gated result is RMS-normed in this many equal parts                                     */
+    const float *head_decay;      /* LINEAR: [heads]: S <- head_decay[h] * S + k v^T                                                  */
+    /* ---- LN_PRE */
+    const float *hc1, *hc2;       /* packed [in (streams) | out (streams) | mix (streams x streams, [from][to])], or NULL: x += y     */
+    const float *branch_norm;     /* [width] or NULL: RMS norm weight of this mixer's projected result (see B200_NORM_LN_PRE)         */
 } b200_hybrid_layer_t;
 
 typedef struct {

@@ -62,7 +62,8 @@ class HybridConfig(C.Structure):
     """b200_hybrid_config_t (include/b200llm.h)."""
     _fields_ = [("width", C.c_int), ("vocab", C.c_int), ("num_layers", C.c_int), ("dtype", C.c_int), ("norm_eps", C.c_float),
                 ("max_tokens", C.c_int), ("max_seqs", C.c_int), ("max_pages_per_seq", C.c_int), ("embed_scale", C.c_float),
-                ("logit_softcap", C.c_float), ("final_norm", C.c_int), ("loop_start", C.c_int), ("loop_stop", C.c_int), ("loop_times", C.c_int)]
+                ("logit_softcap", C.c_float), ("final_norm", C.c_int), ("loop_start", C.c_int), ("loop_stop", C.c_int), ("loop_times", C.c_int),
+                ("logit_scale", C.c_float), ("streams", C.c_int)]
 
 
 class HybridLayer(C.Structure):
@@ -82,7 +83,10 @@ class HybridLayer(C.Structure):
                 ("attn_weight", C.c_int), ("out_gate", C.c_int), ("head_bias", C.c_void_p), ("dist_r1", C.c_void_p), ("dist_r2", C.c_void_p),
                 ("b_in", C.c_void_p), ("b_out", C.c_void_p), ("conv", C.c_int), ("gate_rank", C.c_int), ("conv_w", C.c_void_p),
                 ("a_log", C.c_void_p), ("w_gate2", C.c_void_p), ("gate_cap", C.c_float), ("side", C.c_void_p), ("mix_scale", C.c_float),
-                ("side_scale", C.c_float)]
+                ("side_scale", C.c_float),
+                ("rot_half", C.c_int), ("rot_factor", C.c_float), ("rot_low", C.c_float), ("rot_high", C.c_float), ("rot_original", C.c_float),
+                ("v_norm", C.c_int), ("softcap", C.c_float), ("gate_act", C.c_int), ("conv_b", C.c_void_p), ("skip", C.c_void_p),
+                ("norm_groups", C.c_int), ("head_decay", C.c_void_p), ("hc1", C.c_void_p), ("hc2", C.c_void_p), ("branch_norm", C.c_void_p)]
 
 
 class HybridBatch(C.Structure):
@@ -91,10 +95,10 @@ class HybridBatch(C.Structure):
                 ("seq_pos0", C.c_void_p), ("seq_slot", C.c_void_p), ("block_table", C.c_void_p), ("want_rows", C.c_void_p)]
 
 
-MIXER_ATTN_CHUNKED, MIXER_GLA, MIXER_LATENT, MIXER_ATTN_SCORED, MIXER_DELTA, MIXER_MLSTM = 1, 2, 3, 4, 5, 6
+MIXER_ATTN_CHUNKED, MIXER_GLA, MIXER_LATENT, MIXER_ATTN_SCORED, MIXER_DELTA, MIXER_MLSTM, MIXER_SSD, MIXER_LINEAR = 1, 2, 3, 4, 5, 6, 7, 8
 ATTN_SOFTMAX, ATTN_SIGMOID = 0, 1
 MLP_NONE, MLP_MOE, MLP_DENSE = 0, 1, 2
-NORM_RMS_POST, NORM_DYT_PRE_POST, NORM_LN_PARALLEL = 0, 1, 2
+NORM_RMS_POST, NORM_DYT_PRE_POST, NORM_LN_PARALLEL, NORM_LN_PRE = 0, 1, 2, 3
 ROUTE_SIGMOID, ROUTE_SOFTMAX = 0, 1
 ACT_RELU2, ACT_SILU, ACT_GELU_TANH, ACT_RELU = 0, 1, 2, 3
 (PLAN_MIXED_IDS, PLAN_MIXED_STARTS, PLAN_MIXED_POS0, PLAN_MIXED_SLOTS, PLAN_MIXED_REQUESTS, PLAN_MIXED_BLOCK_TABLE,

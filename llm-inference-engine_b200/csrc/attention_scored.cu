@@ -1,10 +1,11 @@
 // attention_scored.cu -- grouped-query attention over a paged pool of keys [dim] and values [vdim] whose parts are options of the launch
 // (B200_MIXER_ATTN_SCORED), for ragged mixed batches:
 //   * scored_prep_kernel: bias of the q / k / v projections, RMS norm of every q and k head (one weight vector shared by the heads),
-//     rotation of the first rot_dims dimensions of every q and k head in INTERLEAVED pairs (2i, 2i+1) by the angle pos * base^(-2i/rot_dims),
-//     q to a dense buffer, k and v to their pages;
+//     rotation of the first rot_dims dimensions of every q and k head in INTERLEAVED pairs (2i, 2i+1) -- or in halves (i, i + rot_dims/2) --
+//     by the angle pos * base^(-2i/rot_dims), optionally with the long wavelengths slowed down; optionally every value head divided by its
+//     root mean square; q to a dense buffer, k and v to their pages;
 //   * scored_attn_kernel: every token of the batch against the keys of ITS sequence inside the window 0 <= i - j < window (0: all j <= i).
-//     score = scale * q.k - r1[h] * ln(1 + r2[h] * (i - j)) (the penalty is optional); weights either softmax over the visible keys or
+//     score = cap(scale * q.k) - r1[h] * ln(1 + r2[h] * (i - j)) (cap(s) = c tanh(s / c) and the penalty are optional); weights either softmax over the visible keys or
 //     sigmoid(score + head_bias[h]) without any normalisation; optional sigmoid output gate; the result is scaled by out_scale and written
 //     with a row stride, so that several mixers fill one row of a shared output-projection input;
 //   * scored_attn_mma_kernel: the same for prompt portions on the tensor cores (16-bit engines, dim and vdim multiples of 16 up to 128).
@@ -25,12 +26,22 @@ __global__ void __launch_bounds__(256)
 scored_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__restrict__ b_in, T *__restrict__ q_out, T *__restrict__ k_pool,
                    T *__restrict__ v_pool, const float *__restrict__ q_norm, const float *__restrict__ k_norm, float eps,
                    const int *__restrict__ tok_seq, const int *__restrict__ tok_pos, const int *__restrict__ block_table, int mpps, int heads,
-                   int kv_heads, int dim, int vdim, int rot_dims, float rot_base) {
+                   int kv_heads, int dim, int vdim, int rot_dims, float rot_base, ScoredPrepOptions opt) {
     extern __shared__ float rot[];  // cos [rot_dims/2] | sin [rot_dims/2]
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const int pos = tok_pos[t], half = rot_dims / 2;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        const double a = (double)pos * pow((double)rot_base, -2.0 * (double)i / (double)rot_dims);
+        double f = pow((double)rot_base, -2.0 * (double)i / (double)rot_dims);
+        if (opt.rot_factor > 0.0f) {  // long wavelengths turn more slowly, with a smooth band between the two regimes
+            const double wl = 6.283185307179586476925286766559 / f, orig = (double)opt.rot_original;
+            if (wl > orig / (double)opt.rot_low) {
+                f /= (double)opt.rot_factor;
+            } else if (!(wl < orig / (double)opt.rot_high)) {
+                const double sm = (orig / wl - (double)opt.rot_low) / ((double)opt.rot_high - (double)opt.rot_low);
+                f = (1.0 - sm) * f / (double)opt.rot_factor + sm * f;
+            }
+        }
+        const double a = (double)pos * f;
         double s, c;
         sincos(a, &s, &c);
         rot[i] = (float)c, rot[half + i] = (float)s;
@@ -39,7 +50,6 @@ scored_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__
     const T *row = proj + (size_t)t * ld + col0;
     const float *bias = b_in;  // counted from the mixer's own first row
     const int page = block_table[(size_t)tok_seq[t] * mpps + pos / kPageS], off = pos % kPageS;
-    const int npair = (dim + 1) / 2;
     for (int hh = warp; hh < heads + kv_heads; hh += nwarp) {
         const bool is_q = hh < heads;
         const int src = is_q ? hh * dim : heads * dim + (hh - heads) * dim;
@@ -57,25 +67,35 @@ scored_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__
         if (is_q) dst = q_out + ((size_t)t * heads + hh) * dim;
         else if (page >= 0) dst = k_pool + (((size_t)page * kv_heads + (hh - heads)) * kPageS + off) * dim;
         else continue;  // no page held: nothing is written (the host refuses such a batch)
-        for (int p = lane; p < npair; p += 32) {
-            const int c0 = 2 * p, c1 = c0 + 1;
-            float a = Elem<T>::to_f(row[src + c0]) + (bias ? bias[src + c0] : 0.0f);
-            float b = c1 < dim ? Elem<T>::to_f(row[src + c1]) + (bias ? bias[src + c1] : 0.0f) : 0.0f;
-            if (nw) {
-                a = a * inv * nw[c0];
-                if (c1 < dim) b = b * inv * nw[c1];
-            }
-            if (c1 < rot_dims) {
-                const float cs = rot[p], sn = rot[half + p];
-                const float ra = a * cs - b * sn, rb = b * cs + a * sn;
-                a = ra, b = rb;
-            }
-            dst[c0] = Elem<T>::from_f(a);
-            if (c1 < dim) dst[c1] = Elem<T>::from_f(b);
+        auto load = [&](int c) {
+            const float v = Elem<T>::to_f(row[src + c]) + (bias ? bias[src + c] : 0.0f);
+            return nw ? v * inv * nw[c] : v;
+        };
+        for (int p = lane; p < half; p += 32) {  // the rotating pairs: (2p, 2p+1), or (p, p + half)
+            const int c0 = opt.rot_half ? p : 2 * p, c1 = opt.rot_half ? p + half : 2 * p + 1;
+            const float a = load(c0), b = load(c1), cs = rot[p], sn = rot[half + p];
+            dst[c0] = Elem<T>::from_f(a * cs - b * sn);
+            dst[c1] = Elem<T>::from_f(b * cs + a * sn);
         }
+        for (int c = rot_dims + lane; c < dim; c += 32) dst[c] = Elem<T>::from_f(load(c));  // the rest passes unchanged
     }
     if (page < 0) return;
     const int vsrc = (heads + kv_heads) * dim;
+    if (opt.v_norm) {  // every value head is cached divided by its root mean square
+        for (int g = warp; g < kv_heads; g += nwarp) {
+            float ss = 0.0f;
+            for (int c = lane; c < vdim; c += 32) {
+                const float v = Elem<T>::to_f(row[vsrc + g * vdim + c]) + (bias ? bias[vsrc + g * vdim + c] : 0.0f);
+                ss = fmaf(v, v, ss);
+            }
+            const float inv = rsqrtf(warp_sum(ss) / (float)vdim + eps);
+            for (int c = lane; c < vdim; c += 32) {
+                const float v = Elem<T>::to_f(row[vsrc + g * vdim + c]) + (bias ? bias[vsrc + g * vdim + c] : 0.0f);
+                v_pool[(((size_t)page * kv_heads + g) * kPageS + off) * vdim + c] = Elem<T>::from_f(v * inv);
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < kv_heads * vdim; c += blockDim.x) {
         const int g = c / vdim, cc = c - g * vdim;
         const float v = Elem<T>::to_f(row[vsrc + c]) + (bias ? bias[vsrc + c] : 0.0f);
@@ -86,6 +106,11 @@ scored_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 // for weights that are rounded to 16 bits right away: hardware exponential and reciprocal (relative error ~1e-6)
 __device__ __forceinline__ float sigmoid_fast(float z) { return __fdividef(1.0f, 1.0f + __expf(-z)); }
+// tanh(z) = sign(z) (1 - 2 / (exp(2|z|) + 1)) from the hardware exponential and reciprocal: absolute error of a few 1e-7, saturating cleanly
+__device__ __forceinline__ float tanh_fast(float z) {
+    const float e = __expf(2.0f * fabsf(z));
+    return copysignf(1.0f - __fdividef(2.0f, e + 1.0f), z);
+}
 
 // One CTA per (token, query head).  Shared memory: q[dim] | weights[keys] | partial[key groups][vdim] | red[33].
 template <typename T>
@@ -94,7 +119,7 @@ scored_attn_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, const 
                    const float *__restrict__ dist_r1, const float *__restrict__ dist_r2, const T *__restrict__ gate_in, int gate_ld,
                    T *__restrict__ out, int out_ld, float out_scale, const int *__restrict__ tok_seq, const int *__restrict__ tok_pos,
                    const int *__restrict__ block_table, int mpps, int heads, int kv_heads, int dim, int vdim, float scale, int window,
-                   int sigmoid, int max_keys, int part_floats, const int *__restrict__ tok_list) {
+                   int sigmoid, int max_keys, int part_floats, const int *__restrict__ tok_list, float softcap) {
     extern __shared__ float sm[];
     const int t = tok_list ? tok_list[blockIdx.x] : blockIdx.x, h = blockIdx.y;
     const int g = h / (heads / kv_heads);
@@ -137,6 +162,7 @@ scored_attn_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, const 
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
             acc *= scale;
+            if (softcap > 0.0f) acc = softcap * tanhf(acc / softcap);
             if (dist_r1) acc -= r1 * log1pf(r2 * (float)(pos - p));
             if (sigmoid) acc = sigmoid_f(acc + hb);
             if (j < nkeys) {
@@ -278,7 +304,7 @@ __global__ void __launch_bounds__(128)
 scored_attn_mma_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, const T *__restrict__ v_pool, const float *__restrict__ head_bias,
                        const float *__restrict__ dist_r1, const float *__restrict__ dist_r2, const T *__restrict__ gate_in, int gate_ld,
                        T *__restrict__ out, int out_ld, float out_scale, const int4 *__restrict__ tiles, const int *__restrict__ block_table,
-                       int mpps, int heads, int kv_heads, float scale, int window, int pen_len) {
+                       int mpps, int heads, int kv_heads, float scale, int window, int pen_len, float softcap) {
     extern __shared__ __align__(16) unsigned char smraw[];
     T *qs = reinterpret_cast<T *>(smraw);       // [64][DK]
     T *ks = qs + kTileQS * DK;                  // [2][64][DK]
@@ -331,7 +357,10 @@ scored_attn_mma_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, co
     for (int kk = 0; kk < DK / 16; ++kk)
         ldsm4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], qs + swzs<DK>(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kk * 16 + (lane >> 4) * 8));
 
-    const float sl2 = SIG ? scale : scale * kLog2e;
+    // a capped score: cap * tanh(scale * s / cap), in the softmax form times log2(e)
+    const bool capped = softcap > 0.0f;
+    const float sl2 = capped ? scale / softcap : (SIG ? scale : scale * kLog2e), cap2 = SIG ? softcap : softcap * kLog2e;
+    auto scaled = [&](float sv) { return capped ? cap2 * tanh_fast(sv * sl2) : sv * sl2; };
     const float hb = (SIG && head_bias) ? head_bias[h] : 0.0f;
     const bool has_pen = !SIG && dist_r1 != nullptr;
     const int p_a = pos0 + warp * 16 + gid, p_b = p_a + 8;  // rows gid and gid + 8 of this warp's 16
@@ -369,8 +398,8 @@ scored_attn_mma_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, co
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int key = kt * kPageS + j * 8 + tig * 2 + e;
-                    w[e] = (key <= p_a && key >= lo_a) ? sigmoid_fast(fmaf(s[j][e], sl2, hb)) : 0.0f;
-                    w[2 + e] = (key <= p_b && key >= lo_b) ? sigmoid_fast(fmaf(s[j][2 + e], sl2, hb)) : 0.0f;
+                    w[e] = (key <= p_a && key >= lo_a) ? sigmoid_fast(scaled(s[j][e]) + hb) : 0.0f;
+                    w[2 + e] = (key <= p_b && key >= lo_b) ? sigmoid_fast(scaled(s[j][2 + e]) + hb) : 0.0f;
                 }
                 pf[j >> 1][(j & 1) * 2] = pack2s<T>(w[0], w[1]);
                 pf[j >> 1][(j & 1) * 2 + 1] = pack2s<T>(w[2], w[3]);
@@ -383,8 +412,8 @@ scored_attn_mma_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, co
                 for (int e = 0; e < 2; ++e) {
                     const int key = kt * kPageS + j * 8 + tig * 2 + e;
                     const bool va = key <= p_a && key >= lo_a, vb = key <= p_b && key >= lo_b;
-                    s[j][e] = va ? s[j][e] * sl2 - (has_pen ? pen[p_a - key] : 0.0f) : -INFINITY;
-                    s[j][2 + e] = vb ? s[j][2 + e] * sl2 - (has_pen ? pen[p_b - key] : 0.0f) : -INFINITY;
+                    s[j][e] = va ? scaled(s[j][e]) - (has_pen ? pen[p_a - key] : 0.0f) : -INFINITY;
+                    s[j][2 + e] = vb ? scaled(s[j][2 + e]) - (has_pen ? pen[p_b - key] : 0.0f) : -INFINITY;
                     mx_a = fmaxf(mx_a, s[j][e]);
                     mx_b = fmaxf(mx_b, s[j][2 + e]);
                 }
@@ -462,27 +491,28 @@ bool scored_attention_tiles_supported(int dtype, int dim, int vdim, int gate_ld,
 template <typename T, int DK, int DV>
 static int launch_scored_mma_t(const void *q, const void *k_pool, const void *v_pool, const float *head_bias, const float *r1, const float *r2,
                                const void *gate_in, int gate_ld, void *out, int out_ld, float out_scale, const int *tiles, int n_tiles,
-                               const int *block_table, int mpps, int heads, int kv_heads, float scale, int window, int sigmoid, cudaStream_t st) {
+                               const int *block_table, int mpps, int heads, int kv_heads, float scale, int window, int sigmoid, cudaStream_t st,
+                               float softcap) {
     const int pen_len = (!sigmoid && r1) ? window + kTileQS : 0;
     const size_t smem = (size_t)(kTileQS + 2 * kPageS) * DK * sizeof(T) + (size_t)2 * kPageS * DV * sizeof(T) + (size_t)pen_len * sizeof(float);
     auto kern = sigmoid ? scored_attn_mma_kernel<T, DK, DV, 1> : scored_attn_mma_kernel<T, DK, DV, 0>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     kern<<<dim3(n_tiles, heads), 128, smem, st>>>((const T *)q, (const T *)k_pool, (const T *)v_pool, head_bias, r1, r2, (const T *)gate_in, gate_ld,
                                                   (T *)out, out_ld, out_scale, (const int4 *)tiles, block_table, mpps, heads, kv_heads, scale, window,
-                                                  pen_len);
+                                                  pen_len, softcap);
     return cuda_status("scored_attention (tensor core) launch");
 }
 
 int launch_scored_attention_tiles(int dtype, const void *q, const void *k_pool, const void *v_pool, const float *head_bias, const float *dist_r1,
                                   const float *dist_r2, const void *gate_in, int gate_ld, void *out, int out_ld, float out_scale,
                                   const int *tiles, int n_tiles, const int *block_table, int mpps, int heads, int kv_heads, int dim, int vdim,
-                                  float scale, int window, int sigmoid, cudaStream_t st) {
+                                  float scale, int window, int sigmoid, cudaStream_t st, float softcap) {
     if (n_tiles == 0) return B200_OK;
     if (!scored_attention_tiles_supported(dtype, dim, vdim, gate_ld, out_ld, window, dist_r1 != nullptr)) {
         set_error("scored_attention tiles: 16-bit dtypes, dim and vdim of 32 / 64 / 128, a penalty only with a window");
         return B200_ERR_UNSUPPORTED;
     }
-#define B200_SCORED_ARGS q, k_pool, v_pool, head_bias, dist_r1, dist_r2, gate_in, gate_ld, out, out_ld, out_scale, tiles, n_tiles, block_table, mpps, heads, kv_heads, scale, window, sigmoid, st
+#define B200_SCORED_ARGS q, k_pool, v_pool, head_bias, dist_r1, dist_r2, gate_in, gate_ld, out, out_ld, out_scale, tiles, n_tiles, block_table, mpps, heads, kv_heads, scale, window, sigmoid, st, softcap
 #define B200_SCORED_DV(TT, DK)                                                     \
     do {                                                                           \
         if (vdim == 32) return launch_scored_mma_t<TT, DK, 32>(B200_SCORED_ARGS);  \
@@ -504,12 +534,13 @@ int launch_scored_attention_tiles(int dtype, const void *q, const void *k_pool, 
 
 int launch_scored_prep(int dtype, const void *proj, int ld, int col0, const float *b_in, void *q_out, void *k_pool, void *v_pool,
                        const float *q_norm, const float *k_norm, float eps, const int *tok_seq, const int *tok_pos, const int *block_table,
-                       int mpps, int tokens, int heads, int kv_heads, int dim, int vdim, int rot_dims, float rot_base, cudaStream_t st) {
+                       int mpps, int tokens, int heads, int kv_heads, int dim, int vdim, int rot_dims, float rot_base, cudaStream_t st,
+                       ScoredPrepOptions opt) {
     if (tokens == 0) return B200_OK;
     B200_DISPATCH_DTYPE(dtype, {
         scored_prep_kernel<T><<<tokens, 256, (size_t)std::max(rot_dims, 2) * sizeof(float), st>>>(
             (const T *)proj, ld, col0, b_in, (T *)q_out, (T *)k_pool, (T *)v_pool, q_norm, k_norm, eps, tok_seq, tok_pos, block_table, mpps, heads,
-            kv_heads, dim, vdim, rot_dims, rot_base);
+            kv_heads, dim, vdim, rot_dims, rot_base, opt);
     });
     return cuda_status("scored_prep launch");
 }
@@ -517,7 +548,7 @@ int launch_scored_prep(int dtype, const void *proj, int ld, int col0, const floa
 int launch_scored_attention(int dtype, const void *q, const void *k_pool, const void *v_pool, const float *head_bias, const float *dist_r1,
                             const float *dist_r2, const void *gate_in, int gate_ld, void *out, int out_ld, float out_scale, const int *tok_seq,
                             const int *tok_pos, const int *block_table, int mpps, int tokens, int heads, int kv_heads, int dim, int vdim,
-                            float scale, int window, int sigmoid, int max_keys, cudaStream_t st, const int *tok_list) {
+                            float scale, int window, int sigmoid, int max_keys, cudaStream_t st, const int *tok_list, float softcap) {
     if (tokens == 0) return B200_OK;
     const int threads = max_keys >= 512 ? 512 : (max_keys >= 256 ? 256 : 128);  // long contexts: more keys in flight per CTA
     const int ngroups = threads >= vdim ? threads / vdim : 1;
@@ -531,7 +562,7 @@ int launch_scored_attention(int dtype, const void *q, const void *k_pool, const 
         if (smem > 48 * 1024) cudaFuncSetAttribute(scored_attn_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         scored_attn_kernel<T><<<dim3(tokens, heads), threads, smem, st>>>(
             (const T *)q, (const T *)k_pool, (const T *)v_pool, head_bias, dist_r1, dist_r2, (const T *)gate_in, gate_ld, (T *)out, out_ld, out_scale,
-            tok_seq, tok_pos, block_table, mpps, heads, kv_heads, dim, vdim, scale, window, sigmoid, max_keys, (int)part, tok_list);
+            tok_seq, tok_pos, block_table, mpps, heads, kv_heads, dim, vdim, scale, window, sigmoid, max_keys, (int)part, tok_list, softcap);
     });
     return cuda_status("scored_attention launch");
 }

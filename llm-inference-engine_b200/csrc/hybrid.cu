@@ -16,7 +16,11 @@
 //   moe:              router + shared gate (fp32) -> route -> plan -> gather (weight on the input) -> grouped up (+act) -> grouped down
 //                     shared expert: b200_linear up -> act -> b200_linear down
 //                     combine (sum of the token's expert rows + gate * shared) + post-norm + residual add, one kernel
-// and at the end: final norm of the wanted rows -> LM head with fp32 logits.
+// Pre-norm layers on residual streams (B200_NORM_LN_PRE): per sublayer ONE kernel rewrites all streams from the sublayer's result (two
+// mixers side by side arrive as two projected rows, each RMS-normed over the width) and leaves the next sublayer's layer-normed input:
+//   input projection -> mixer (scored attention | delta rule | state-space | linear attention; a second mixer beside it) -> output
+//   projection(s) -> streams + next norm;  gate|up projection -> act(gate) * up -> down projection -> streams + next norm
+// and at the end: final norm of the wanted rows -> LM head with fp32 logits (scaled, soft-capped).
 // Everything is stream-ordered and allocation-free; the only host->device traffic of a call is one copy of the batch description.
 #include "hybrid_ops.cuh"
 
@@ -286,8 +290,11 @@ final_dyt_rows_kernel(const float *__restrict__ x, const int *__restrict__ rows,
     }
 }
 
-__global__ void softcap_kernel(float *__restrict__ logits, size_t n, float cap) {
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) logits[i] = cap * tanhf(logits[i] / cap);
+__global__ void softcap_kernel(float *__restrict__ logits, size_t n, float scale, float cap) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = logits[i] * scale;
+        logits[i] = cap > 0.0f ? cap * tanhf(v / cap) : v;
+    }
 }
 
 template <typename T>
@@ -540,6 +547,94 @@ final_ln_rows_kernel(const float *__restrict__ x, const int *__restrict__ rows, 
     }
 }
 
+// ---- pre-norm layers on residual streams (B200_NORM_LN_PRE)
+// One sublayer's residual step on S streams xs [tokens, S, width] and whatever the next sublayer reads, in one kernel:
+//   y[t, :]   = ya[t, :]                                                     (one projected row), or
+//             = sa * rmsnorm(ya[t, :]) * na + sb * rmsnorm(yb[t, :]) * nb       (two mixers side by side, each normed over the width);
+//   xs[t, v]  = sum_s mix[s][v] * xs[t, s] + out[v] * y[t, :]   for all v at once (hc packed [in | out | mix]; NULL: xs += y), or, with
+//               x_init, every stream = x_init[t, :] (the embedding output; no y);
+//   sum_out / trace [t, :] = sum_v xs[t, v];
+//   h_out[t, :] = T(layernorm(sum_v in_next[v] * xs[t, v]; ln_next))              (hc_next packed alike; NULL: the one stream itself).
+// Everything is fp32; the row waits in shared memory between the passes (mean first, then the squared deviations).
+constexpr int kMaxStreams = 8;
+template <typename T>
+__global__ void __launch_bounds__(256)
+stream_residual_kernel(float *__restrict__ xs, int S, const float *__restrict__ x_init, const T *__restrict__ ya, const T *__restrict__ yb,
+                       const float *__restrict__ na, const float *__restrict__ nb, float sa, float sb, const float *__restrict__ hc,
+                       const float *__restrict__ hc_next, const float *__restrict__ ln_next, float eps, int width, T *__restrict__ h_out,
+                       float *__restrict__ sum_out, float *__restrict__ trace) {
+    extern __shared__ __align__(16) float row[];  // [width]
+    __shared__ float red[33];
+    __shared__ float c_out[kMaxStreams], c_in[kMaxStreams], c_mix[kMaxStreams * kMaxStreams];
+    const int t = blockIdx.x;
+    if (threadIdx.x < S) {
+        c_out[threadIdx.x] = hc ? hc[S + threadIdx.x] : 1.0f;
+        c_in[threadIdx.x] = hc_next ? hc_next[threadIdx.x] : 1.0f;
+    }
+    if (threadIdx.x < S * S) c_mix[threadIdx.x] = hc ? hc[2 * S + threadIdx.x] : (threadIdx.x / S == threadIdx.x % S ? 1.0f : 0.0f);
+    float ia = 1.0f, ib = 1.0f;
+    if (ya && na) {  // (uniform over the CTA)
+        float ssa = 0.0f, ssb = 0.0f;
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            const float a = Elem<T>::to_f(ya[(size_t)t * width + c]);
+            ssa = fmaf(a, a, ssa);
+            if (yb) {
+                const float b = Elem<T>::to_f(yb[(size_t)t * width + c]);
+                ssb = fmaf(b, b, ssb);
+            }
+        }
+        ia = sa * rsqrtf(block_sum(ssa, red) / (float)width + eps);
+        if (yb) ib = sb * rsqrtf(block_sum(ssb, red) / (float)width + eps);
+    }
+    __syncthreads();
+    float sum = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float y = 0.0f;
+        if (ya) {
+            y = Elem<T>::to_f(ya[(size_t)t * width + c]);
+            if (na) {
+                y *= ia * na[c];
+                if (yb) y = fmaf(Elem<T>::to_f(yb[(size_t)t * width + c]) * ib, nb[c], y);
+            }
+        }
+        float old[kMaxStreams];
+#pragma unroll
+        for (int v = 0; v < kMaxStreams; ++v)
+            if (v < S) old[v] = x_init ? x_init[(size_t)t * width + c] : xs[((size_t)t * S + v) * width + c];
+        float u = 0.0f, total = 0.0f;
+#pragma unroll
+        for (int v = 0; v < kMaxStreams; ++v) {
+            if (v >= S) break;
+            float a;
+            if (x_init) {
+                a = old[v];
+            } else {
+                a = c_out[v] * y;
+#pragma unroll
+                for (int q = 0; q < kMaxStreams; ++q)
+                    if (q < S) a = fmaf(c_mix[q * S + v], old[q], a);
+            }
+            if (x_init || ya) xs[((size_t)t * S + v) * width + c] = a;
+            total += a;
+            u = fmaf(c_in[v], a, u);
+        }
+        if (trace) trace[(size_t)t * width + c] = total;
+        if (sum_out) sum_out[(size_t)t * width + c] = total;
+        row[c] = u;
+        sum += u;
+    }
+    if (!h_out) return;
+    const float mean = block_sum(sum, red) / (float)width;
+    float sq = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float dv = row[c] - mean;
+        sq = fmaf(dv, dv, sq);
+    }
+    const float inv = rsqrtf(block_sum(sq, red) / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+        h_out[(size_t)t * width + c] = Elem<T>::from_f(fmaf((row[c] - mean) * inv, ln_next[c], ln_next[width + c]));
+}
+
 // where one mixer of one layer run keeps what it remembers
 struct MixerPlan {
     size_t k_off = 0, v_off = 0;      // attention kinds: byte offsets into the kv pool (set by set_pools); LATENT: k_off of the rows it reads
@@ -572,7 +667,7 @@ struct b200_hybrid {
     float *x = nullptr, *f32a = nullptr, *f32b = nullptr, *xn = nullptr;
     void *h = nullptr, *proj = nullptr, *mix = nullptr, *mix2 = nullptr, *y = nullptr, *xg = nullptr, *u = nullptr, *yrows = nullptr, *us = nullptr,
          *ys = nullptr, *lqn = nullptr, *lqr = nullptr, *lql = nullptr, *lol = nullptr, *lov = nullptr;
-    float *lpart = nullptr, *rec = nullptr, *f32c = nullptr;
+    float *lpart = nullptr, *rec = nullptr, *f32c = nullptr, *xs = nullptr;
     void *cat = nullptr, *xc = nullptr;
     int *meta = nullptr, *moe_i = nullptr;
     float *moe_f = nullptr;
@@ -582,14 +677,23 @@ struct b200_hybrid {
 namespace {
 
 struct Carve {
-    size_t x, f32a, f32b, xn, h, proj, mix, y, xg, u, yrows, us, ys, lqn, lqr, lql, lov, lpart, meta, moe_i, moe_f, rec, f32c, cat, xc, total;
+    size_t x, f32a, f32b, xn, h, proj, mix, y, xg, u, yrows, us, ys, lqn, lqr, lql, lov, lpart, meta, moe_i, moe_f, rec, f32c, cat, xc, xs, total;
 };
 
 // rows of the input projection and columns of the output projection that ONE mixer owns
 int mixer_rows(const b200_hybrid_layer_t &l) {
     if (l.mixer == B200_MIXER_ATTN_SCORED) return (l.heads + l.kv_heads) * l.dim + l.kv_heads * l.vdim + (l.out_gate ? l.heads * l.vdim : 0);
-    if (l.mixer == B200_MIXER_DELTA) return 2 * l.kv_heads * l.dim + l.heads * l.vdim + l.heads + l.decay_rank + l.gate_rank;
+    if (l.mixer == B200_MIXER_DELTA)
+        return 2 * l.kv_heads * l.dim + l.heads * l.vdim + l.heads + (l.decay_rank > 0 ? l.decay_rank + l.gate_rank : l.heads + l.heads * l.vdim);
     if (l.mixer == B200_MIXER_MLSTM) return 2 * l.heads * l.dim + 2 * l.heads * l.vdim + 2 * l.heads;
+    if (l.mixer == B200_MIXER_SSD) return 2 * l.heads * l.vdim + 2 * l.kv_heads * l.dim + l.heads;
+    if (l.mixer == B200_MIXER_LINEAR) return 2 * l.heads * l.dim + 2 * l.heads * l.vdim;
+    return 0;
+}
+// channels of the short convolution whose last inputs are part of the state
+int conv_channels(const b200_hybrid_layer_t &l) {
+    if (l.mixer == B200_MIXER_DELTA) return 2 * l.kv_heads * l.dim + l.heads * l.vdim;
+    if (l.mixer == B200_MIXER_SSD) return l.heads * l.vdim + 2 * l.kv_heads * l.dim;
     return 0;
 }
 int cat_cols(const b200_hybrid_layer_t &l) {
@@ -598,6 +702,8 @@ int cat_cols(const b200_hybrid_layer_t &l) {
 int rec_cols(const b200_hybrid_layer_t &l) {
     if (l.mixer == B200_MIXER_DELTA) return delta_row(l.heads, l.kv_heads, l.dim, l.vdim).ld;
     if (l.mixer == B200_MIXER_MLSTM) return mlstm_row(l.heads, l.dim, l.vdim).ld;
+    if (l.mixer == B200_MIXER_SSD) return decay_row(l.heads, l.kv_heads, l.dim, l.vdim).ld;
+    if (l.mixer == B200_MIXER_LINEAR) return decay_row(l.heads, l.heads, l.dim, l.vdim).ld;
     return 0;
 }
 
@@ -608,6 +714,7 @@ int max_rows_of(const b200_hybrid_config_t &c, const b200_hybrid_layer_t &l) {
 
 int n_in_of(const b200_hybrid_layer_t &l) {
     if (l.norm == B200_NORM_LN_PARALLEL) return mixer_rows(l) + (l.side ? mixer_rows(*l.side) : 0) + (l.mlp == B200_MLP_DENSE ? 2 * l.expert_ff : 0);
+    if (l.norm == B200_NORM_LN_PRE) return mixer_rows(l) + (l.side ? mixer_rows(*l.side) : 0);
     if (l.mixer == B200_MIXER_ATTN_CHUNKED) return (2 * l.heads + l.kv_heads) * l.dim;
     if (l.mixer == B200_MIXER_LATENT) return l.heads * (l.dim + l.rot_dim) + l.heads * l.vdim + (l.kv_from < 0 ? l.kv_rank + l.rot_dim : 0);
     return 2 * l.heads * l.dim + 2 * l.heads * l.vdim + l.decay_rank;
@@ -618,6 +725,7 @@ Carve carve(const b200_hybrid *m) {
     const size_t T = (size_t)c.max_tokens, es = c.dtype == B200_F32 ? 4 : 2;
     size_t n_in = 1, n_mix = 1, n_f32 = 1, rows = 0, ff = 1, sff = 1, experts = 1, top = 1, lqn = 0, lqr = 0, lql = 0, lov = 0, lheads = 0, lpart = 0;
     size_t n_rec = 0, n_heads = 0, n_cat = 0;
+    bool pre_norm = false;
     const size_t t_pad = (T + 127) / 128 * 128;  // rows per head of the latent mixer's grouped GEMMs
     for (int i = 0; i < c.num_layers; ++i) {
         if (!m->layer_set[i]) continue;
@@ -626,8 +734,9 @@ Carve carve(const b200_hybrid *m) {
         n_mix = std::max(n_mix, (size_t)l.heads * std::max(l.dim, l.vdim));
         n_f32 = std::max(n_f32, (size_t)l.heads * std::max(l.dim, l.vdim));
         n_mix = std::max(n_mix, (size_t)l.heads * l.vdim);
-        if (l.norm == B200_NORM_LN_PARALLEL) {
-            n_cat = std::max(n_cat, (size_t)cat_cols(l));
+        if (l.norm == B200_NORM_LN_PARALLEL || l.norm == B200_NORM_LN_PRE) {
+            if (l.norm == B200_NORM_LN_PARALLEL) n_cat = std::max(n_cat, (size_t)cat_cols(l));
+            else n_cat = std::max(n_cat, (size_t)l.heads * l.vdim), sff = std::max(sff, (size_t)3 * l.expert_ff), pre_norm = true;
             for (const b200_hybrid_layer_t *mx : {&l, l.side}) {
                 if (!mx) continue;
                 n_mix = std::max(n_mix, (size_t)mx->heads * std::max(mx->dim, mx->vdim));
@@ -680,8 +789,9 @@ Carve carve(const b200_hybrid *m) {
     // moe floats: sel_weight [T*top] | row_weight [rows] | shared_gate [T]
     k.moe_f = align256((T * top + rows + T) * 4);
     k.rec = align256(T * n_rec * 4), k.f32c = align256(2 * T * n_heads * 4), k.cat = align256(T * n_cat * es);
-    k.xc = c.loop_times > 0 ? align256(2 * T * c.width * es) : 0;
-    k.total = k.x + k.f32a + k.f32b + k.xn + k.h + k.proj + 2 * k.mix + k.y + k.xg + k.u + k.yrows + k.us + k.ys + k.lqn + k.lqr + 2 * k.lql +
+    k.xc = (c.loop_times > 0 && !pre_norm) ? align256(2 * T * c.width * es) : 0;
+    k.xs = pre_norm ? align256(T * (size_t)std::max(c.streams, 1) * c.width * 4) : 0;
+    k.total = k.xs + k.x + k.f32a + k.f32b + k.xn + k.h + k.proj + 2 * k.mix + k.y + k.xg + k.u + k.yrows + k.us + k.ys + k.lqn + k.lqr + 2 * k.lql +
               k.lov + k.lpart + k.meta + k.moe_i + k.moe_f + k.rec + k.f32c + k.cat + k.xc;
     return k;
 }
@@ -698,6 +808,10 @@ b200_hybrid_t *b200_hybrid_create(const b200_hybrid_config_t *cfg) {
     if (!cfg || cfg->width <= 0 || cfg->vocab <= 0 || cfg->num_layers <= 0 || cfg->max_tokens <= 0 || cfg->max_seqs <= 0 ||
         cfg->max_pages_per_seq <= 0 || (cfg->dtype != B200_F32 && cfg->dtype != B200_F16 && cfg->dtype != B200_BF16)) {
         set_error("hybrid_create: bad configuration");
+        return nullptr;
+    }
+    if (cfg->streams < 0 || cfg->streams > kMaxStreams) {
+        set_error("hybrid_create: %d residual streams outside [1, %d]", cfg->streams, kMaxStreams);
         return nullptr;
     }
     b200_hybrid *m = new (std::nothrow) b200_hybrid();
@@ -739,10 +853,17 @@ static int check_scored_mixer(const b200_hybrid_layer_t *w) {
         B200_REQUIRE((w->q_norm == nullptr) == (w->k_norm == nullptr), "hybrid_set_layer: q and k are normed together or not at all");
     } else if (w->mixer == B200_MIXER_DELTA) {
         B200_REQUIRE(w->kv_heads > 0 && w->heads % w->kv_heads == 0, "hybrid_set_layer: heads %d not a multiple of kv_heads %d", w->heads, w->kv_heads);
-        B200_REQUIRE(w->conv >= 1 && w->conv <= 64 && w->conv_w && w->decay_rank > 0 && w->gate_rank > 0 && w->w_decay && w->w_gate2 && w->a_log && w->out_norm,
-                     "hybrid_set_layer: delta-rule sizes / weights missing");
+        B200_REQUIRE(w->conv >= 1 && w->conv <= 64 && w->conv_w && w->a_log && w->out_norm && w->decay_rank >= 0, "hybrid_set_layer: delta-rule sizes / weights missing");
+        if (w->decay_rank > 0) B200_REQUIRE(w->gate_rank > 0 && w->w_decay && w->w_gate2, "hybrid_set_layer: the delta rule's low-rank halves are missing");
     } else if (w->mixer == B200_MIXER_MLSTM) {
         B200_REQUIRE(w->out_norm && w->gate_cap >= 0.0f, "hybrid_set_layer: matrix-memory weights missing");
+    } else if (w->mixer == B200_MIXER_SSD) {
+        B200_REQUIRE(w->kv_heads > 0 && w->heads % w->kv_heads == 0, "hybrid_set_layer: heads %d not a multiple of the %d groups", w->heads, w->kv_heads);
+        B200_REQUIRE(w->conv >= 1 && w->conv <= 64 && w->conv_w && w->a_log && w->out_norm, "hybrid_set_layer: state-space sizes / weights missing");
+        B200_REQUIRE(w->norm_groups >= 1 && (w->heads * w->vdim) % w->norm_groups == 0, "hybrid_set_layer: %d norm groups do not divide %d channels",
+                     w->norm_groups, w->heads * w->vdim);
+    } else if (w->mixer == B200_MIXER_LINEAR) {
+        B200_REQUIRE(w->head_decay && w->out_norm, "hybrid_set_layer: linear-attention weights missing");
     } else {
         set_error("hybrid_set_layer: mixer kind %d cannot share a norm with the feed-forward", w->mixer);
         return B200_ERR_INVALID_ARG;
@@ -753,20 +874,28 @@ static int check_scored_mixer(const b200_hybrid_layer_t *w) {
 int b200_hybrid_set_layer(b200_hybrid_t *m, int layer, const b200_hybrid_layer_t *w) {
     B200_REQUIRE(m && w, "hybrid_set_layer: null argument");
     B200_REQUIRE(layer >= 0 && layer < m->cfg.num_layers, "hybrid_set_layer: layer %d outside [0, %d)", layer, m->cfg.num_layers);
-    B200_REQUIRE(w->mixer >= B200_MIXER_ATTN_CHUNKED && w->mixer <= B200_MIXER_MLSTM, "hybrid_set_layer: unknown mixer kind %d", w->mixer);
-    B200_REQUIRE(w->norm >= B200_NORM_RMS_POST && w->norm <= B200_NORM_LN_PARALLEL, "hybrid_set_layer: unknown norm kind %d", w->norm);
+    B200_REQUIRE(w->mixer >= B200_MIXER_ATTN_CHUNKED && w->mixer <= B200_MIXER_LINEAR, "hybrid_set_layer: unknown mixer kind %d", w->mixer);
+    B200_REQUIRE(w->norm >= B200_NORM_RMS_POST && w->norm <= B200_NORM_LN_PRE, "hybrid_set_layer: unknown norm kind %d", w->norm);
     B200_REQUIRE(w->heads > 0 && w->dim > 0 && w->w_in && w->w_out, "hybrid_set_layer: mixer sizes / weights missing");
-    if (w->norm == B200_NORM_LN_PARALLEL) {
-        // one norm, one input projection, one output projection; the mixers are of the kinds that read a shared projection
+    if (w->norm == B200_NORM_LN_PARALLEL || w->norm == B200_NORM_LN_PRE) {
+        // LN_PARALLEL: one norm, one input projection, one output projection; the mixers are of the kinds that read a shared projection
+        const bool pre = w->norm == B200_NORM_LN_PRE;
         B200_REQUIRE(w->pre1, "hybrid_set_layer: norm parameters missing");
         int rc = check_scored_mixer(w);
         if (rc != B200_OK) return rc;
+        if (!pre) B200_REQUIRE(w->mixer != B200_MIXER_SSD && w->mixer != B200_MIXER_LINEAR, "hybrid_set_layer: mixer kind %d needs the pre-norm layer form", w->mixer);
         if (w->side) {
             B200_REQUIRE(!w->side->side, "hybrid_set_layer: a second mixer has no second mixer of its own");
             if ((rc = check_scored_mixer(w->side)) != B200_OK) return rc;
+            if (pre) B200_REQUIRE(w->side->w_out && (w->branch_norm == nullptr) == (w->side->branch_norm == nullptr),
+                                  "hybrid_set_layer: the second mixer needs its output projection, and both mixers a norm of their results or neither");
         }
         B200_REQUIRE(w->mlp == B200_MLP_NONE || (w->mlp == B200_MLP_DENSE && w->gated && w->expert_ff > 0),
-                     "hybrid_set_layer: beside a mixer under one norm the feed-forward is a gated dense one or none");
+                     "hybrid_set_layer: the feed-forward of this layer form is a gated dense one or none");
+        if (pre) {
+            B200_REQUIRE(w->mlp == B200_MLP_NONE || (w->pre2 && w->w_up && w->w_down), "hybrid_set_layer: feed-forward norm / weights missing");
+            B200_REQUIRE(std::max(m->cfg.streams, 1) == 1 || (w->hc1 && (w->mlp == B200_MLP_NONE || w->hc2)), "hybrid_set_layer: stream coefficients missing");
+        }
         B200_REQUIRE(w->act >= B200_ACT_RELU2 && w->act <= B200_ACT_RELU, "hybrid_set_layer: unknown activation %d", w->act);
         m->layers[layer] = *w;
         if (w->side) {
@@ -779,8 +908,8 @@ int b200_hybrid_set_layer(b200_hybrid_t *m, int layer, const b200_hybrid_layer_t
         m->scratch = nullptr;
         return B200_OK;
     }
-    B200_REQUIRE(w->mixer <= B200_MIXER_LATENT && !w->side, "hybrid_set_layer: mixer kind %d needs the shared-norm layer form", w->mixer);
-    B200_REQUIRE(m->cfg.loop_times == 0, "hybrid_set_layer: only shared-norm layers can be looped");
+    B200_REQUIRE(w->mixer <= B200_MIXER_LATENT && !w->side, "hybrid_set_layer: mixer kind %d needs the shared-norm or the pre-norm layer form", w->mixer);
+    B200_REQUIRE(m->cfg.loop_times == 0, "hybrid_set_layer: only shared-norm and pre-norm layers can be looped");
     if (w->norm == B200_NORM_RMS_POST) B200_REQUIRE(w->norm1, "hybrid_set_layer: norm weight missing");
     else B200_REQUIRE(w->pre1 && w->post1, "hybrid_set_layer: norm parameters missing");
     if (w->mixer == B200_MIXER_ATTN_CHUNKED) {
@@ -875,6 +1004,7 @@ int b200_hybrid_set_scratch(b200_hybrid_t *m, void *ptr, size_t bytes) {
     m->f32c = (float *)p, p += k.f32c;
     m->cat = p, p += k.cat;
     m->xc = p, p += k.xc;
+    m->xs = (float *)p, p += k.xs;
     return B200_OK;
 }
 
@@ -892,8 +1022,8 @@ void place_mixer(const b200_hybrid_layer_t &l, size_t es, int num_pages, int num
         if (l.kv_from < 0) p.k_off = kv, kv += align256((size_t)num_pages * kPageH * (l.kv_rank + l.rot_dim) * es);
     } else {
         p.state_off = stt, stt += align256((size_t)num_slots * l.heads * l.dim * l.vdim * 4);
-        if (l.mixer == B200_MIXER_DELTA) {
-            p.aux_off = stt, stt += align256((size_t)num_slots * std::max(l.conv - 1, 1) * (2 * l.kv_heads * l.dim + l.heads * l.vdim) * 4);
+        if (l.mixer == B200_MIXER_DELTA || l.mixer == B200_MIXER_SSD) {
+            p.aux_off = stt, stt += align256((size_t)num_slots * std::max(l.conv - 1, 1) * conv_channels(l) * 4);
         } else if (l.mixer == B200_MIXER_MLSTM) {
             p.aux_off = stt, stt += align256((size_t)num_slots * l.heads * l.dim * 4);
             p.aux2_off = stt, stt += align256((size_t)num_slots * l.heads * 4);
@@ -1053,9 +1183,11 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
     // 16-bit engines: every kernel that writes the residual stream also writes its 16-bit copy h, which the next projections read
     const int n_runs = (int)m->plan.size();
     const bool shared_norm = m->layers[0].norm == B200_NORM_LN_PARALLEL;  // layers of one norm whose sublayers share the projections
+    const bool pre_norm = m->layers[0].norm == B200_NORM_LN_PRE;          // pre-norm layers on residual streams
     for (int i = 0; i < c.num_layers; ++i)
-        B200_REQUIRE((m->layers[i].norm == B200_NORM_LN_PARALLEL) == shared_norm, "hybrid_forward: shared-norm layers and others do not mix in one model");
-    if (c.loop_times > 0 && (!m->w_entry || !m->loop_step)) {
+        B200_REQUIRE((m->layers[i].norm == B200_NORM_LN_PARALLEL) == shared_norm && (m->layers[i].norm == B200_NORM_LN_PRE) == pre_norm,
+                     "hybrid_forward: shared-norm layers, pre-norm layers and others do not mix in one model");
+    if (shared_norm && c.loop_times > 0 && (!m->w_entry || !m->loop_step)) {
         set_error("hybrid_forward: the looped block's entry weights are not set");
         return B200_ERR_STATE;
     }
@@ -1080,51 +1212,125 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
                                                     c.vocab, c.embed_scale != 0.0f ? c.embed_scale : 1.0f);
         });
         RUN(hand_over(0, nullptr, nullptr, nullptr));
+    } else if (pre_norm) {
+        B200_DISPATCH_DTYPE(dt, {
+            embed_rows_kernel<T><<<NT, 128, 0, st>>>(d_ids, (const T *)m->embedding, m->x, (T *)nullptr, 0, width, c.vocab, c.embed_scale != 0.0f ? c.embed_scale : 1.0f);
+        });
     } else {
     B200_DISPATCH_DTYPE(dt, { embed_f32_kernel<T><<<NT, 128, 0, st>>>(d_ids, (const T *)m->embedding, m->x, f32 ? nullptr : (T *)m->h, width, c.vocab,
                                                                       c.embed_scale != 0.0f ? c.embed_scale : 1.0f); });
     }
 
-    // one mixer of a shared-norm layer: reads its rows of the projection from column `col`, writes its heads at column `ocol` of the
-    // output projection's input row, scaled
-    auto run_mixer = [&](const b200_hybrid_layer_t &l, const MixerPlan &mp, int n_in, int col, int n_cat, int ocol, float out_scale) -> int {
-        char *out = (char *)m->cat + (size_t)ocol * es;
+    // one mixer of a shared-norm or pre-norm layer: reads its rows of the projection from column `col`, writes its heads into rows of `out`
+    // (row stride out_ld: several mixers may fill one row of a shared output projection's input), scaled
+    auto run_mixer = [&](const b200_hybrid_layer_t &l, const MixerPlan &mp, int n_in, int col, void *out_buf, int out_ld, float out_scale) -> int {
+        char *out = (char *)out_buf;
+        const int one_token = gla_kinds == kGlaOneToken;
         if (l.mixer == B200_MIXER_ATTN_SCORED) {
             const char *gate = l.out_gate ? (const char *)m->proj + (size_t)(col + (l.heads + l.kv_heads) * l.dim + l.kv_heads * l.vdim) * es : nullptr;
             char *kp = m->kv_pool + mp.k_off, *vp = m->kv_pool + mp.v_off;
             const int sig = l.attn_weight == B200_ATTN_SIGMOID;
+            ScoredPrepOptions opt;
+            opt.rot_half = l.rot_half, opt.rot_factor = l.rot_factor, opt.rot_low = l.rot_low, opt.rot_high = l.rot_high, opt.rot_original = l.rot_original;
+            opt.v_norm = l.v_norm;
             RUN(launch_scored_prep(dt, m->proj, n_in, col, l.b_in, m->mix, kp, vp, l.q_norm, l.k_norm, c.norm_eps, d_seq, d_pos, d_bt, mpps, NT, l.heads,
-                                   l.kv_heads, l.dim, l.vdim, l.rot_dims, l.rot_base, st));
+                                   l.kv_heads, l.dim, l.vdim, l.rot_dims, l.rot_base, st, opt));
             const int max_keys = l.window > 0 ? std::min(l.window, mpps * kPageH) : mpps * kPageH;
-            if (scored_attention_tiles_supported(dt, l.dim, l.vdim, n_in, n_cat, l.window, l.dist_r1 != nullptr)) {
-                RUN(launch_scored_attention_tiles(dt, m->mix, kp, vp, l.head_bias, l.dist_r1, l.dist_r2, gate, n_in, out, n_cat, out_scale, d_tiles, n_tiles,
-                                                  d_bt, mpps, l.heads, l.kv_heads, l.dim, l.vdim, l.scale, l.window, sig, st));
-                RUN(launch_scored_attention(dt, m->mix, kp, vp, l.head_bias, l.dist_r1, l.dist_r2, gate, n_in, out, n_cat, out_scale, d_seq, d_pos, d_bt,
-                                            mpps, n_short, l.heads, l.kv_heads, l.dim, l.vdim, l.scale, l.window, sig, max_keys, st, d_short));
+            if (scored_attention_tiles_supported(dt, l.dim, l.vdim, n_in, out_ld, l.window, l.dist_r1 != nullptr)) {
+                RUN(launch_scored_attention_tiles(dt, m->mix, kp, vp, l.head_bias, l.dist_r1, l.dist_r2, gate, n_in, out, out_ld, out_scale, d_tiles, n_tiles,
+                                                  d_bt, mpps, l.heads, l.kv_heads, l.dim, l.vdim, l.scale, l.window, sig, st, l.softcap));
+                RUN(launch_scored_attention(dt, m->mix, kp, vp, l.head_bias, l.dist_r1, l.dist_r2, gate, n_in, out, out_ld, out_scale, d_seq, d_pos, d_bt,
+                                            mpps, n_short, l.heads, l.kv_heads, l.dim, l.vdim, l.scale, l.window, sig, max_keys, st, d_short, l.softcap));
             } else {
-                RUN(launch_scored_attention(dt, m->mix, kp, vp, l.head_bias, l.dist_r1, l.dist_r2, gate, n_in, out, n_cat, out_scale, d_seq, d_pos, d_bt,
-                                            mpps, NT, l.heads, l.kv_heads, l.dim, l.vdim, l.scale, l.window, sig, max_keys, st));
+                RUN(launch_scored_attention(dt, m->mix, kp, vp, l.head_bias, l.dist_r1, l.dist_r2, gate, n_in, out, out_ld, out_scale, d_seq, d_pos, d_bt,
+                                            mpps, NT, l.heads, l.kv_heads, l.dim, l.vdim, l.scale, l.window, sig, max_keys, st, nullptr, l.softcap));
             }
         } else if (l.mixer == B200_MIXER_DELTA) {
             float *conv_state = (float *)(m->state_pool + mp.aux_off);
             const DeltaRow lay = delta_row(l.heads, l.kv_heads, l.dim, l.vdim);
-            RUN(launch_delta_prep(dt, m->proj, n_in, col, l.conv_w, l.conv, conv_state, l.w_decay, l.decay_bias, l.a_log, l.decay_rank, l.w_gate2,
-                                  l.gate_rank, m->mix2, m->f32a, m->f32b, m->rec, d_seq, d_pos, d_pos0, d_slot, NT, l.heads, l.kv_heads, l.dim, l.vdim, st));
-            RUN(launch_conv_state_update(dt, m->proj, n_in, col, conv_state, l.conv, 2 * l.kv_heads * l.dim + l.heads * l.vdim, d_start, d_pos0, d_slot, S, st));
+            if (l.decay_rank > 0)
+                RUN(launch_delta_prep(dt, m->proj, n_in, col, l.conv_w, l.conv, conv_state, l.w_decay, l.decay_bias, l.a_log, l.decay_rank, l.w_gate2,
+                                      l.gate_rank, m->mix2, m->f32a, m->f32b, m->rec, d_seq, d_pos, d_pos0, d_slot, NT, l.heads, l.kv_heads, l.dim, l.vdim, st));
+            else
+                RUN(launch_delta_prep_direct(dt, m->proj, n_in, col, l.conv_w, l.conv, conv_state, l.decay_bias, l.a_log, m->rec, d_seq, d_pos, d_pos0, d_slot,
+                                             NT, l.heads, l.kv_heads, l.dim, l.vdim, st));
+            RUN(launch_conv_state_update(dt, m->proj, n_in, col, conv_state, l.conv, conv_channels(l), d_start, d_pos0, d_slot, S, st));
             RUN(launch_delta_recurrent(m->rec, (float *)(m->state_pool + mp.state_off), m->f32b, d_start, d_pos0, d_slot, S, l.heads, l.kv_heads, l.dim,
-                                       l.vdim, st, gla_kinds == kGlaOneToken));
-            RUN(launch_head_output(dt, m->f32b, nullptr, nullptr, l.out_norm, 0, c.norm_eps, m->rec + lay.gate, lay.ld, nullptr, 0, out, n_cat, out_scale, NT,
-                                   l.heads, l.vdim, st));
+                                       l.vdim, st, one_token));
+            if (l.decay_rank > 0) {
+                RUN(launch_head_output(dt, m->f32b, nullptr, nullptr, l.out_norm, 0, c.norm_eps, m->rec + lay.gate, lay.ld, nullptr, 0, out, out_ld, out_scale,
+                                       NT, l.heads, l.vdim, st, l.gate_act));
+            } else {  // the gate's pre-activations are rows of the projection
+                const char *gate = (const char *)m->proj + (size_t)(col + conv_channels(l) + 2 * l.heads) * es;
+                RUN(launch_head_output(dt, m->f32b, nullptr, nullptr, l.out_norm, 0, c.norm_eps, nullptr, 0, gate, n_in, out, out_ld, out_scale, NT, l.heads,
+                                       l.vdim, st, l.gate_act));
+            }
+        } else if (l.mixer == B200_MIXER_SSD) {
+            // z | x | B | C | dt: the convolution runs over x | B | C; the recurrence's key side is B (per group), its query side C
+            float *conv_state = (float *)(m->state_pool + mp.aux_off);
+            const int inner = l.heads * l.vdim;
+            const DecayRow lay = decay_row(l.heads, l.kv_heads, l.dim, l.vdim);
+            RUN(launch_ssd_prep(dt, m->proj, n_in, col, l.conv_w, l.conv_b, l.conv, conv_state, l.decay_bias, l.a_log, l.skip, m->rec, d_seq, d_pos, d_pos0,
+                                d_slot, NT, l.heads, l.kv_heads, l.dim, l.vdim, st));
+            RUN(launch_conv_state_update(dt, m->proj, n_in, col + inner, conv_state, l.conv, conv_channels(l), d_start, d_pos0, d_slot, S, st));
+            RUN(launch_decay_recurrent(m->rec, (float *)(m->state_pool + mp.state_off), m->f32b, d_start, d_pos0, d_slot, S, l.heads, l.kv_heads, l.dim,
+                                       l.vdim, st, one_token));
+            RUN(launch_group_output(dt, m->f32b, m->rec + lay.skip, lay.ld, l.out_norm, c.norm_eps, (const char *)m->proj + (size_t)col * es, n_in, 1, 1, out,
+                                    out_ld, NT, inner, l.norm_groups, st));
+        } else if (l.mixer == B200_MIXER_LINEAR) {
+            const int inner = l.heads * l.vdim;
+            RUN(launch_linear_prep(dt, m->proj, n_in, col, l.head_decay, m->rec, NT, l.heads, l.dim, l.vdim, st));
+            RUN(launch_decay_recurrent(m->rec, (float *)(m->state_pool + mp.state_off), m->f32b, d_start, d_pos0, d_slot, S, l.heads, l.heads, l.dim, l.vdim,
+                                       st, one_token));
+            RUN(launch_group_output(dt, m->f32b, nullptr, 0, l.out_norm, c.norm_eps, (const char *)m->proj + (size_t)(col + 2 * l.heads * l.dim + inner) * es,
+                                    n_in, 0, 0, out, out_ld, NT, inner, 1, st));
         } else {
             const char *gate = (const char *)m->proj + (size_t)(col + 2 * l.heads * l.dim + l.heads * l.vdim) * es;
             float *nq = m->f32c, *mo = m->f32c + (size_t)NT * l.heads;
             RUN(launch_mlstm_prep(dt, m->proj, n_in, col, l.b_in, l.gate_cap, m->rec, NT, l.heads, l.dim, l.vdim, st));
             RUN(launch_mlstm_recurrent(m->rec, (float *)(m->state_pool + mp.state_off), (float *)(m->state_pool + mp.aux_off),
-                                       (float *)(m->state_pool + mp.aux2_off), m->f32b, nq, mo, d_start, d_pos0, d_slot, S, l.heads, l.dim, l.vdim, st, gla_kinds == kGlaOneToken));
-            RUN(launch_head_output(dt, m->f32b, nq, mo, l.out_norm, l.vdim, c.norm_eps, nullptr, 0, gate, n_in, out, n_cat, out_scale, NT, l.heads, l.vdim, st));
+                                       (float *)(m->state_pool + mp.aux2_off), m->f32b, nq, mo, d_start, d_pos0, d_slot, S, l.heads, l.dim, l.vdim, st, one_token));
+            RUN(launch_head_output(dt, m->f32b, nq, mo, l.out_norm, l.vdim, c.norm_eps, nullptr, 0, gate, n_in, out, out_ld, out_scale, NT, l.heads, l.vdim, st));
         }
         return B200_OK;
     };
+    // ---- pre-norm layers on residual streams
+    const int n_streams = std::max(c.streams, 1);
+    // the residual step of one sublayer + the layer-normed input of the sublayer that follows (hc_next / ln_next; none after the last run)
+    auto stream_step = [&](const float *x_init, const void *ya, const void *yb, const float *na, const float *nb, float sa, float sb, const float *hc,
+                           const float *hc_next, const float *ln_next, float *sum_out, float *trace) -> int {
+        B200_DISPATCH_DTYPE(dt, {
+            stream_residual_kernel<T><<<NT, 256, (size_t)width * sizeof(float), st>>>(m->xs, n_streams, x_init, (const T *)ya, (const T *)yb, na, nb, sa, sb, hc,
+                                                                                    hc_next, ln_next, c.norm_eps, width, ln_next ? (T *)m->h : nullptr, sum_out, trace);
+        });
+        return cuda_status("stream_residual launch");
+    };
+    auto pre_norm_layer = [&](int run) -> int {
+        const LayerPlan &lp = m->plan[run];
+        const b200_hybrid_layer_t &l = m->layers[lp.layer];
+        const b200_hybrid_layer_t *next = run + 1 < n_runs ? &m->layers[m->plan[run + 1].layer] : nullptr;
+        const bool last = next == nullptr, ff = l.mlp == B200_MLP_DENSE;
+        float *trace = layer_trace ? layer_trace + (size_t)run * NT * width : nullptr;
+        RUN(linear(m, m->h, l.w_in, m->proj, NT, width, lp.n_in, st));
+        // every mixer has an output projection of its own: the first writes its heads to `cat`, the second to `mix2`
+        RUN(run_mixer(l, lp, lp.n_in, 0, m->cat, l.heads * l.vdim, 1.0f));
+        RUN(linear(m, m->cat, l.w_out, m->y, NT, l.heads * l.vdim, width, st));
+        if (l.side) {
+            RUN(run_mixer(*l.side, lp.side, lp.n_in, mixer_rows(l), m->mix2, l.side->heads * l.side->vdim, 1.0f));
+            RUN(linear(m, m->mix2, l.side->w_out, m->ys, NT, l.side->heads * l.side->vdim, width, st));
+        }
+        RUN(stream_step(nullptr, m->y, l.side ? m->ys : nullptr, l.branch_norm, l.side ? l.side->branch_norm : nullptr, l.side ? l.mix_scale : 1.0f,
+                        l.side ? l.side_scale : 1.0f, l.hc1, ff ? l.hc2 : (next ? next->hc1 : nullptr), ff ? l.pre2 : (next ? next->pre1 : nullptr),
+                        (!ff && last) ? m->x : nullptr, ff ? nullptr : trace));
+        if (!ff) return B200_OK;
+        char *up = (char *)m->us, *act = up + (size_t)NT * 2 * l.expert_ff * es;
+        RUN(linear(m, m->h, l.w_up, up, NT, width, 2 * l.expert_ff, st));
+        RUN(launch_gated_activation(dt, up, act, NT, l.expert_ff, l.act, nullptr, 0, st));
+        RUN(linear(m, act, l.w_down, m->ys, NT, l.expert_ff, width, st));
+        return stream_step(nullptr, m->ys, nullptr, nullptr, nullptr, 1.0f, 1.0f, l.hc2, next ? next->hc1 : nullptr, next ? next->pre1 : nullptr,
+                           last ? m->x : nullptr, trace);
+    };
+    if (pre_norm) RUN(stream_step(m->x, nullptr, nullptr, nullptr, nullptr, 1.0f, 1.0f, nullptr, m->layers[m->plan[0].layer].hc1, m->layers[m->plan[0].layer].pre1, nullptr, nullptr));
     // a shared-norm layer run: (entry step) -> one input projection -> mixers and the gated inner row side by side -> one output
     // projection -> residual + the next run's normed input
     auto shared_norm_layer = [&](int run) -> int {
@@ -1140,10 +1346,10 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
         const int n_cat = cat_cols(l);
         RUN(linear(m, m->h, l.w_in, m->proj, NT, width, lp.n_in, st));
         int col = 0, ocol = 0;
-        RUN(run_mixer(l, lp, lp.n_in, col, n_cat, ocol, l.side ? l.mix_scale : 1.0f));
+        RUN(run_mixer(l, lp, lp.n_in, col, (char *)m->cat + (size_t)ocol * es, n_cat, l.side ? l.mix_scale : 1.0f));
         col += mixer_rows(l), ocol += l.heads * l.vdim;
         if (l.side) {
-            RUN(run_mixer(*l.side, lp.side, lp.n_in, col, n_cat, ocol, l.side_scale));
+            RUN(run_mixer(*l.side, lp.side, lp.n_in, col, (char *)m->cat + (size_t)ocol * es, n_cat, l.side_scale));
             col += mixer_rows(*l.side), ocol += l.side->heads * l.side->vdim;
         }
         if (l.mlp == B200_MLP_DENSE) {
@@ -1198,6 +1404,10 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
     for (int li = 0; li < n_runs; ++li) {  // (only shared-norm layers loop: elsewhere a run is its layer)
         if (shared_norm) {
             RUN(shared_norm_layer(li));
+            continue;
+        }
+        if (pre_norm) {
+            RUN(pre_norm_layer(li));
             continue;
         }
         const b200_hybrid_layer_t &l = m->layers[li];
@@ -1357,16 +1567,17 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
     if (W > 0) {
         // the wanted rows only: final norm (fp32 and, for 16-bit engines, a 16-bit copy in h), then the LM head with fp32 logits
         B200_DISPATCH_DTYPE(dt, {
-            if (c.final_norm == B200_NORM_LN_PARALLEL) final_ln_rows_kernel<T><<<W, 256, 0, st>>>(m->x, d_want, m->final_norm, c.norm_eps, m->xn, f32 ? nullptr : (T *)m->h, width);
+            if (c.final_norm == B200_NORM_LN_PARALLEL || c.final_norm == B200_NORM_LN_PRE) final_ln_rows_kernel<T><<<W, 256, 0, st>>>(m->x, d_want, m->final_norm, c.norm_eps, m->xn, f32 ? nullptr : (T *)m->h, width);
             else if (c.final_norm == B200_NORM_DYT_PRE_POST) final_dyt_rows_kernel<T><<<W, 256, 0, st>>>(m->x, d_want, m->final_norm, m->xn, f32 ? nullptr : (T *)m->h, width);
             else final_norm_rows_kernel<T><<<W, 256, 0, st>>>(m->x, d_want, m->final_norm, c.norm_eps, m->xn, f32 ? nullptr : (T *)m->h, width);
         });
         rc = launch_dense_f32out(dt, m->h, m->lm_head, logits, W, c.vocab, width, st);
         if (rc == B200_ERR_UNSUPPORTED) rc = launch_proj_f32(B200_F32, m->xn, width, dt, m->lm_head, nullptr, logits, c.vocab, W, c.vocab, width, st);
         if (rc != B200_OK) return rc;
-        if (c.logit_softcap > 0.0f) {
+        const float lscale = c.logit_scale != 0.0f ? c.logit_scale : 1.0f;
+        if (c.logit_softcap > 0.0f || lscale != 1.0f) {
             const size_t n = (size_t)W * c.vocab;
-            softcap_kernel<<<(unsigned)std::min<size_t>((n + 255) / 256, 148 * 8), 256, 0, st>>>(logits, n, c.logit_softcap);
+            softcap_kernel<<<(unsigned)std::min<size_t>((n + 255) / 256, 148 * 8), 256, 0, st>>>(logits, n, lscale, c.logit_softcap);
         }
     }
 #undef RUN

@@ -36,24 +36,31 @@ int launch_latent_gate(int dtype, const void *ov, const void *gate_in, int gate_
 
 // attention_scored.cu: proj [tokens, ld] holds q (heads*dim), k (kv_heads*dim), v (kv_heads*vdim) from column col0 on; b_in (optional) is
 // counted from the same row.  q_out [tokens, heads*dim]; pools K [pages, kv_heads, page, dim], V [pages, kv_heads, page, vdim]
+// options of the prep step: rot_half: rotating pairs (i, i + rot_dims/2) instead of (2i, 2i+1); rot_factor > 0: long wavelengths are slowed
+// down (b200_hybrid_layer_t); v_norm: value heads are cached divided by their root mean square
+struct ScoredPrepOptions { int rot_half = 0; float rot_factor = 0.0f, rot_low = 0.0f, rot_high = 0.0f, rot_original = 0.0f; int v_norm = 0; };
 int launch_scored_prep(int dtype, const void *proj, int ld, int col0, const float *b_in, void *q_out, void *k_pool, void *v_pool,
                        const float *q_norm, const float *k_norm, float eps, const int *tok_seq, const int *tok_pos, const int *block_table,
-                       int mpps, int tokens, int heads, int kv_heads, int dim, int vdim, int rot_dims, float rot_base, cudaStream_t st);
+                       int mpps, int tokens, int heads, int kv_heads, int dim, int vdim, int rot_dims, float rot_base, cudaStream_t st,
+                       ScoredPrepOptions opt = ScoredPrepOptions());
 int launch_scored_attention(int dtype, const void *q, const void *k_pool, const void *v_pool, const float *head_bias, const float *dist_r1,
                             const float *dist_r2, const void *gate_in, int gate_ld, void *out, int out_ld, float out_scale, const int *tok_seq,
                             const int *tok_pos, const int *block_table, int mpps, int tokens, int heads, int kv_heads, int dim, int vdim,
-                            float scale, int window, int sigmoid, int max_keys, cudaStream_t st, const int *tok_list = nullptr);
+                            float scale, int window, int sigmoid, int max_keys, cudaStream_t st, const int *tok_list = nullptr,
+                            float softcap = 0.0f);
 bool scored_attention_tiles_supported(int dtype, int dim, int vdim, int gate_ld, int out_ld, int window, bool penalty);
 int launch_scored_attention_tiles(int dtype, const void *q, const void *k_pool, const void *v_pool, const float *head_bias, const float *dist_r1,
                                   const float *dist_r2, const void *gate_in, int gate_ld, void *out, int out_ld, float out_scale,
                                   const int *tiles, int n_tiles, const int *block_table, int mpps, int heads, int kv_heads, int dim, int vdim,
-                                  float scale, int window, int sigmoid, cudaStream_t st);
+                                  float scale, int window, int sigmoid, cudaStream_t st, float softcap = 0.0f);
 
 // recurrent.cu: column offsets of the fp32 row per token that the prep kernels write and the recurrences read.
 // launch_delta_prep scratch: lr (engine dtype) of tokens * (rank + gate_rank) elements + 256 bytes, za fp32 [tokens, heads*dim], zg fp32
 // [tokens, heads*vdim]
 struct DeltaRow { int q, k, v, decay, gate, beta, ld; };
 struct MlstmRow { int q, k, v, gi, gf, ld; };
+struct DecayRow { int q, k, v, skip, decay, ld; };  // q, k [kv_heads*dim] | v, skip [heads*vdim] | decay [heads]
+DecayRow decay_row(int heads, int kv_heads, int dim, int vdim);
 DeltaRow delta_row(int heads, int kv_heads, int dim, int vdim);
 MlstmRow mlstm_row(int heads, int dim, int vdim);
 int launch_delta_prep(int dtype, const void *proj, int ld, int col0, const float *conv_w, int taps, float *conv_state, const void *w_decay,
@@ -72,7 +79,26 @@ int launch_mlstm_recurrent(const float *rec, float *S, float *n_state, float *m_
 // out[t, h*vdim + j] = out_scale * y * rsqrt(mean_j y^2 + eps) * w[h*w_stride + j] * sigmoid(gate); y = o, or o / (max(|nq|, exp(-m)) + 1e-6)
 int launch_head_output(int dtype, const float *o, const float *nq, const float *m_in, const float *w, int w_stride, float eps,
                        const float *gate_f, int gate_f_ld, const void *gate_t, int gate_t_ld, void *out, int out_ld, float out_scale, int tokens,
-                       int heads, int vdim, cudaStream_t st);
+                       int heads, int vdim, cudaStream_t st, int gate_act = 0);
+// the delta rule with one decay per head and full-rank gates: proj row q | k | v | step (heads) | decay-in (heads) | gate (heads*vdim)
+int launch_delta_prep_direct(int dtype, const void *proj, int ld, int col0, const float *conv_w, int taps, float *conv_state,
+                             const float *decay_bias, const float *a_log, float *rec, const int *tok_seq, const int *tok_pos,
+                             const int *seq_pos0, const int *seq_slot, int tokens, int heads, int kv_heads, int dim, int vdim, cudaStream_t st);
+// the state-space mixer: proj row z | x (heads*vdim each) | B | C (groups*state each) | dt (heads); conv_state [slots, taps - 1, channels]
+// over the channels x | B | C; writes the tokens' DecayRow (kv_heads = groups, dim = state)
+int launch_ssd_prep(int dtype, const void *proj, int ld, int col0, const float *conv_w, const float *conv_b, int taps, float *conv_state,
+                    const float *dt_bias, const float *a_log, const float *skip_w, float *rec, const int *tok_seq, const int *tok_pos,
+                    const int *seq_pos0, const int *seq_slot, int tokens, int heads, int groups, int state, int vdim, cudaStream_t st);
+// linear attention with a constant decay per head: proj row q | k (heads*dim each) | v | gate (heads*vdim each); writes the DecayRow
+int launch_linear_prep(int dtype, const void *proj, int ld, int col0, const float *head_decay, float *rec, int tokens, int heads, int dim, int vdim,
+                       cudaStream_t st);
+// S <- decay S + k v^T;  o = S^T q over every sequence's portion, from the tokens' DecayRow
+int launch_decay_recurrent(const float *rec, float *S, float *o, const int *seq_start, const int *seq_pos0, const int *seq_slot, int n_seqs,
+                           int heads, int kv_heads, int dim, int vdim, cudaStream_t st, int one_token = 0);
+// out[t, c] = T((o + skip)[t, c] (* act(gate) if gate_first) * rsqrt(mean over the column's group + eps) * w[c] (* act(gate) if not)),
+// `groups` equal groups of the `cols` columns; act = sigmoid (gate_act 0) or silu (1); skip may be NULL
+int launch_group_output(int dtype, const float *o, const float *skip, int skip_ld, const float *w, float eps, const void *gate, int gate_ld,
+                        int gate_act, int gate_first, void *out, int out_ld, int tokens, int cols, int groups, cudaStream_t st);
 
 // gla.cu
 // decay[t, c] = sigmoid(z)^(1/tau), z = w_decay[c, :] . proj[t, col0 : col0 + rank] + bias[c]   (fp32 from the projection on)

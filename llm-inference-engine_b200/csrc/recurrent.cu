@@ -8,7 +8,12 @@
 //         m' = max(f + m, i);   S <- exp(f + m - m') S + exp(i - m') k v^T;   n likewise with k alone;
 //         o = S^T q / (max(|n . q|, exp(-m')) + 1e-6)
 //     then o / rms(o) * w * sigmoid(gate).
-// Both recurrences are independent per COLUMN of S (one value channel): column_recurrence_kernel gives every column to one thread (or to
+//   * decayed outer-product memory with ONE decay per head and token:  S <- a S + k v^T;  o = S^T q.  Two mixers are this recurrence
+//     behind different prep steps: the state-space mixer (B200_MIXER_SSD: convolution + silu on x | B | C, step size dt = softplus(z + b),
+//     a = exp(-exp(a_log) dt), k = B, v = dt x, q = C, plus a skip term) and linear attention with a constant decay per head
+//     (B200_MIXER_LINEAR: q, k, v = silu of their projections).  The gated delta rule with one decay per head and full-rank gates takes
+//     delta_prep_direct_kernel and the delta recurrence.
+// All recurrences are independent per COLUMN of S (one value channel): column_recurrence_kernel gives every column to one thread (or to
 // LANES adjacent threads for long key vectors) that keeps it in registers for the whole portion; the per-token key-side vectors are
 // staged in shared memory and read as broadcasts.  The normaliser n of the matrix memory is carried as one more column whose value is 1.
 // Everything from the projections' outputs on is fp32.
@@ -30,6 +35,12 @@ DeltaRow delta_row(int heads, int kv_heads, int dim, int vdim) {
     DeltaRow r;
     r.q = 0, r.k = r.q + pad4(kv_heads * dim), r.v = r.k + pad4(kv_heads * dim), r.decay = r.v + pad4(heads * vdim);
     r.gate = r.decay + pad4(heads * dim), r.beta = r.gate + pad4(heads * vdim), r.ld = r.beta + pad4(heads);
+    return r;
+}
+DecayRow decay_row(int heads, int kv_heads, int dim, int vdim) {
+    DecayRow r;
+    r.q = 0, r.k = r.q + pad4(kv_heads * dim), r.v = r.k + pad4(kv_heads * dim), r.skip = r.v + pad4(heads * vdim);
+    r.decay = r.skip + pad4(heads * vdim), r.ld = r.decay + pad4(heads);
     return r;
 }
 MlstmRow mlstm_row(int heads, int dim, int vdim) {
@@ -86,6 +97,151 @@ delta_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__r
     }
     for (int c = threadIdx.x; c < nv; c += blockDim.x) out[lay.v + c] = cv[2 * nqk + c];
     for (int h = threadIdx.x; h < heads; h += blockDim.x) out[lay.beta + h] = sigmoid_r(Elem<T>::to_f(row[h]));
+}
+
+// The causal convolution of channel c at token t (packed row) / position pos: taps - 1 earlier inputs come from the portion's own rows,
+// from the slot's stored inputs (positions before pos0) or are zero (before position 0).  Every tap reads both places at an index that
+// always exists and keeps the one that is meant.
+template <typename T>
+__device__ __forceinline__ float conv_at(const T *__restrict__ proj, int ld, int col, int t, int pos, int pos0, const float *__restrict__ w, int taps,
+                                         const float *__restrict__ cst, int channels, int c) {
+    const int keep = taps > 1 ? taps - 1 : 1;
+    float acc = 0.0f;
+    for (int j = 0; j < taps; ++j) {
+        const int back = taps - 1 - j, pp = pos - back;
+        const float xp = Elem<T>::to_f(proj[(size_t)max(t - back, 0) * ld + col + c]);
+        const float xs = cst[(size_t)min(max(pp - (pos0 - (taps - 1)), 0), keep - 1) * channels + c];
+        const float x = pp >= pos0 ? xp : (pp >= 0 ? xs : 0.0f);
+        acc = fmaf(w[(size_t)c * taps + j], x, acc);
+    }
+    return acc;
+}
+
+// The delta rule with full-rank gates and one decay per head.  proj row from col0: q | k (kv_heads*dim each) | v (heads*vdim) | step
+// (heads) | decay-in (heads) | gate (heads*vdim; read by the output kernel).  Writes q, k (unit vectors), v, the step and the decay
+// exp(-exp(a_log[h]) * softplus(decay-in[h] + bias[h])), repeated over the head's key channels, into the token's fp32 row.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+delta_prep_direct_kernel(const T *__restrict__ proj, int ld, int col0, const float *__restrict__ conv_w, int taps, const float *__restrict__ conv_state,
+                         const float *__restrict__ decay_bias, const float *__restrict__ a_log, float *__restrict__ rec, DeltaRow lay,
+                         const int *__restrict__ tok_seq, const int *__restrict__ tok_pos, const int *__restrict__ seq_pos0,
+                         const int *__restrict__ seq_slot, int heads, int kv_heads, int dim, int vdim) {
+    extern __shared__ float sh[];  // conv outputs [channels]
+    const int t = blockIdx.x, s = tok_seq[t], pos = tok_pos[t], pos0 = seq_pos0[s], slot = seq_slot[s];
+    const int nqk = kv_heads * dim, nv = heads * vdim, channels = 2 * nqk + nv;
+    const float *cst = conv_state + (size_t)slot * (taps - 1) * channels;
+#pragma unroll 4
+    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+        const float acc = conv_at<T>(proj, ld, col0, t, pos, pos0, conv_w, taps, cst, channels, c);
+        sh[c] = acc * sigmoid_r(acc);
+    }
+    __syncthreads();
+    const T *row = proj + (size_t)t * ld + col0 + channels;  // step | decay-in | gate
+    float *out = rec + (size_t)t * lay.ld;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    for (int hh = warp; hh < 2 * kv_heads; hh += nwarp) {  // unit vectors: q heads, then k heads
+        const float *src = sh + hh * dim;
+        float ss = 0.0f;
+        for (int c = lane; c < dim; c += 32) ss = fmaf(src[c], src[c], ss);
+        const bool is_q = hh < kv_heads;
+        const float inv = rsqrtf(warp_sum(ss) + 1e-6f) * (is_q ? rsqrtf((float)dim) : 1.0f);
+        float *dst = out + (is_q ? lay.q + hh * dim : lay.k + (hh - kv_heads) * dim);
+        for (int c = lane; c < dim; c += 32) dst[c] = src[c] * inv;
+    }
+    for (int c = threadIdx.x; c < nv; c += blockDim.x) out[lay.v + c] = sh[2 * nqk + c];
+    for (int h = threadIdx.x; h < heads; h += blockDim.x) out[lay.beta + h] = sigmoid_r(Elem<T>::to_f(row[h]));
+    for (int c = threadIdx.x; c < heads * dim; c += blockDim.x) {
+        const int h = c / dim;
+        const float z = Elem<T>::to_f(row[heads + h]) + (decay_bias ? decay_bias[h] : 0.0f);
+        out[lay.decay + c] = expf(-expf(a_log[h]) * softplus_r(z));
+    }
+}
+
+// The state-space mixer's prep.  proj row from col0: z | x (heads*vdim each) | B | C (groups*state each) | dt (heads).  x | B | C pass the
+// convolution (+ bias) and silu.  Writes the token's fp32 row: q = C, k = B, v = dt * x, skip = skip_w[h] * x, decay = exp(-exp(a_log) dt),
+// dt = softplus(dt-in + dt_bias), unclamped.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+ssd_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__restrict__ conv_w, const float *__restrict__ conv_b, int taps,
+                const float *__restrict__ conv_state, const float *__restrict__ dt_bias, const float *__restrict__ a_log,
+                const float *__restrict__ skip_w, float *__restrict__ rec, DecayRow lay, const int *__restrict__ tok_seq,
+                const int *__restrict__ tok_pos, const int *__restrict__ seq_pos0, const int *__restrict__ seq_slot, int heads, int groups,
+                int state, int vdim) {
+    extern __shared__ float sh[];  // dt [heads]
+    const int t = blockIdx.x, s = tok_seq[t], pos = tok_pos[t], pos0 = seq_pos0[s], slot = seq_slot[s];
+    const int inner = heads * vdim, gn = groups * state, channels = inner + 2 * gn;
+    const float *cst = conv_state + (size_t)slot * (taps - 1) * channels;
+    const T *row = proj + (size_t)t * ld + col0;
+    float *out = rec + (size_t)t * lay.ld;
+    for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+        const float dt = softplus_r(Elem<T>::to_f(row[2 * inner + 2 * gn + h]) + (dt_bias ? dt_bias[h] : 0.0f));
+        sh[h] = dt;
+        out[lay.decay + h] = expf(-expf(a_log[h]) * dt);
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+        float acc = conv_at<T>(proj, ld, col0 + inner, t, pos, pos0, conv_w, taps, cst, channels, c);
+        if (conv_b) acc += conv_b[c];
+        const float v = acc * sigmoid_r(acc);
+        if (c < inner) {
+            const int h = c / vdim;
+            out[lay.v + c] = sh[h] * v;
+            out[lay.skip + c] = skip_w ? skip_w[h] * v : 0.0f;
+        } else if (c < inner + gn) {
+            out[lay.k + (c - inner)] = v;
+        } else {
+            out[lay.q + (c - inner - gn)] = v;
+        }
+    }
+}
+
+// Linear attention with a constant decay per head.  proj row from col0: q | k (heads*dim each) | v | gate (heads*vdim each).
+template <typename T>
+__global__ void __launch_bounds__(256)
+linear_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__restrict__ head_decay, float *__restrict__ rec, DecayRow lay,
+                   int heads, int dim, int vdim) {
+    const int t = blockIdx.x, nqk = heads * dim, nv = heads * vdim;
+    const T *row = proj + (size_t)t * ld + col0;
+    float *out = rec + (size_t)t * lay.ld;
+    for (int c = threadIdx.x; c < nqk; c += blockDim.x) {
+        const float q = Elem<T>::to_f(row[c]), k = Elem<T>::to_f(row[nqk + c]);
+        out[lay.q + c] = q * sigmoid_r(q);
+        out[lay.k + c] = k * sigmoid_r(k);
+    }
+    for (int c = threadIdx.x; c < nv; c += blockDim.x) {
+        const float v = Elem<T>::to_f(row[2 * nqk + c]);
+        out[lay.v + c] = v * sigmoid_r(v);
+    }
+    for (int h = threadIdx.x; h < heads; h += blockDim.x) out[lay.decay + h] = head_decay[h];
+}
+
+// One CTA per (token, group): the read-out of a whole token (or of one of `groups` equal parts of it) normed together.
+//   y_c = o[t, c] + skip[t * skip_ld + c];   gate_first: y_c *= act(gate_c);   out[t, c] = T(y_c * rsqrt(mean_c y^2 + eps) * w[c] * (gate_first
+//   ? 1 : act(gate_c))), act = silu (gate_act 1) or sigmoid (0); c runs over the group's columns of the row of `cols`.
+template <typename T>
+__global__ void __launch_bounds__(256)
+group_output_kernel(const float *__restrict__ o, const float *__restrict__ skip, int skip_ld, const float *__restrict__ w, float eps,
+                    const T *__restrict__ gate, int gate_ld, int gate_act, int gate_first, T *__restrict__ out, int out_ld, int cols, int groups) {
+    __shared__ float red[33];
+    const int t = blockIdx.x / groups, g = blockIdx.x - t * groups, per = cols / groups, c0 = g * per;
+    auto act = [&](float z) { return gate_act ? z * sigmoid_r(z) : sigmoid_r(z); };
+    auto value = [&](int c) {
+        float y = o[(size_t)t * cols + c] + (skip ? skip[(size_t)t * skip_ld + c] : 0.0f);
+        if (gate_first) y *= act(Elem<T>::to_f(gate[(size_t)t * gate_ld + c]));
+        return y;
+    };
+    float ss = 0.0f;
+    for (int c = c0 + threadIdx.x; c < c0 + per; c += blockDim.x) {
+        const float y = value(c);
+        ss = fmaf(y, y, ss);
+    }
+    const float inv = rsqrtf(block_sum(ss, red) / (float)per + eps);
+    for (int c = c0 + threadIdx.x; c < c0 + per; c += blockDim.x) {
+        float y = value(c) * inv * w[c];
+        if (!gate_first) y *= act(Elem<T>::to_f(gate[(size_t)t * gate_ld + c]));
+        out[(size_t)t * out_ld + c] = Elem<T>::from_f(y);
+    }
 }
 
 // za fp32 [tokens, heads*dim] = w_decay . decay-in, zg fp32 [tokens, heads*vdim] = w_gate2 . gate-in (the products of the two low-rank
@@ -153,7 +309,8 @@ mlstm_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__r
 // is read once for the thread's CPT columns, the columns' chains run side by side, and dot products over the rows end in a butterfly over
 // the lanes.  The host picks LANES by how many columns the batch has: one long prompt spreads every column group over many threads (the
 // token loop is sequential, its length per token is RPT), a decode batch of many sequences keeps longer pieces of a column in one thread.
-// MODE 0 (delta): per token k, q, decay [dim] and the step;  MODE 1 (matrix memory): per token k, q [dim] and the two log gates.
+// MODE 0 (delta): per token k, q, decay [dim] and the step;  MODE 1 (matrix memory): per token k, q [dim] and the two log gates;
+// MODE 2 (decayed outer products): per token k, q [dim] and one decay.
 // Shared memory, two stages of kRecTB tokens: per token [NV * DP key-side values (zero beyond dim) | 4 scalars], then v [kRecTB][CB].  The
 // next stage arrives by cp.async while the current one is consumed.
 constexpr int kRecTB = 16;
@@ -301,10 +458,15 @@ column_recurrence_kernel(const float *__restrict__ rec, int rec_ld, int q_off, i
                         }
                 }
             } else {
-                const float gi = sb[tt * TS + NV * DP], gf = sb[tt * TS + NV * DP + 1];
-                const float m_new = fmaxf(gf + m, gi);
-                const float a = expf(gf + m - m_new), b = expf(gi - m_new);
-                m = m_new;
+                float a, b;
+                if (MODE == 1) {
+                    const float gi = sb[tt * TS + NV * DP], gf = sb[tt * TS + NV * DP + 1];
+                    const float m_new = fmaxf(gf + m, gi);
+                    a = expf(gf + m - m_new), b = expf(gi - m_new);
+                    m = m_new;
+                } else {
+                    a = sb[tt * TS + NV * DP], b = 1.0f;
+                }
                 float bv[CPT];
 #pragma unroll
                 for (int c = 0; c < CPT; ++c) bv[c] = b * v[c];
@@ -351,13 +513,13 @@ column_recurrence_kernel(const float *__restrict__ rec, int rec_ld, int q_off, i
     if (MODE == 1 && sub == 0 && col <= vdim && vdim < col + CPT) m_state[(size_t)slot * heads + h] = m;
 }
 
-// One warp per (token, head): out[t, h*vdim + j] = out_scale * y_j * rsqrt(mean_j y^2 + eps) * w[h * w_stride + j] * sigmoid(gate),
+// One warp per (token, head): out[t, h*vdim + j] = out_scale * y_j * rsqrt(mean_j y^2 + eps) * w[h * w_stride + j] * sigmoid(gate) (gate_act 1: silu),
 // y = o (delta) or o / (max(|nq|, exp(-m)) + 1e-6) (matrix memory: nq != NULL).  gate: fp32 pre-activations (gate_f) or the projection's.
 template <typename T>
 __global__ void __launch_bounds__(256)
 head_output_kernel(const float *__restrict__ o, const float *__restrict__ nq, const float *__restrict__ m_in, const float *__restrict__ w,
                    int w_stride, float eps, const float *__restrict__ gate_f, int gate_f_ld, const T *__restrict__ gate_t, int gate_t_ld,
-                   T *__restrict__ out, int out_ld, float out_scale, int tokens, int heads, int vdim) {
+                   T *__restrict__ out, int out_ld, float out_scale, int tokens, int heads, int vdim, int gate_act) {
     const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (idx >= tokens * heads) return;
     const int t = idx / heads, h = idx - t * heads;
@@ -372,7 +534,7 @@ head_output_kernel(const float *__restrict__ o, const float *__restrict__ nq, co
     const float inv = rsqrtf(warp_sum(ss) / (float)vdim + eps) * inv_den;
     for (int j = lane; j < vdim; j += 32) {
         const float z = gate_f ? gate_f[(size_t)t * gate_f_ld + h * vdim + j] : Elem<T>::to_f(gate_t[(size_t)t * gate_t_ld + h * vdim + j]);
-        out[(size_t)t * out_ld + h * vdim + j] = Elem<T>::from_f(src[j] * inv * w[h * w_stride + j] * sigmoid_r(z) * out_scale);
+        out[(size_t)t * out_ld + h * vdim + j] = Elem<T>::from_f(src[j] * inv * w[h * w_stride + j] * (gate_act ? z * sigmoid_r(z) : sigmoid_r(z)) * out_scale);
     }
 }
 
@@ -421,7 +583,7 @@ static int launch_colrec(const float *rec, int rec_ld, int q_off, int k_off, int
         return B200_ERR_UNSUPPORTED;
     }
     const int dp = dim <= 16 ? 16 : (dim <= 32 ? 32 : (dim <= 64 ? 64 : (dim <= 128 ? 128 : (dim <= 256 ? 256 : 512))));
-    const int ncols = vdim + MODE;
+    const int ncols = vdim + (MODE == 1 ? 1 : 0);
     // one column per thread: measured against tiles of four columns (fewer shared-memory reads per multiply-add, but a quarter of the threads),
     // the single column won at every batch shape but one: the token loop is bound by its chain of dependent steps, not by its loads
     constexpr int cpt = 1;
@@ -503,14 +665,67 @@ int launch_mlstm_recurrent(const float *rec, float *S, float *n_state, float *m_
 
 int launch_head_output(int dtype, const float *o, const float *nq, const float *m_in, const float *w, int w_stride, float eps,
                        const float *gate_f, int gate_f_ld, const void *gate_t, int gate_t_ld, void *out, int out_ld, float out_scale, int tokens,
-                       int heads, int vdim, cudaStream_t st) {
+                       int heads, int vdim, cudaStream_t st, int gate_act) {
     if (tokens == 0) return B200_OK;
     const int grid = (tokens * heads + 7) / 8;
     B200_DISPATCH_DTYPE(dtype, {
         head_output_kernel<T><<<grid, 256, 0, st>>>(o, nq, m_in, w, w_stride, eps, gate_f, gate_f_ld, (const T *)gate_t, gate_t_ld, (T *)out, out_ld,
-                                                   out_scale, tokens, heads, vdim);
+                                                   out_scale, tokens, heads, vdim, gate_act);
     });
     return cuda_status("head_output launch");
+}
+
+int launch_delta_prep_direct(int dtype, const void *proj, int ld, int col0, const float *conv_w, int taps, float *conv_state,
+                             const float *decay_bias, const float *a_log, float *rec, const int *tok_seq, const int *tok_pos,
+                             const int *seq_pos0, const int *seq_slot, int tokens, int heads, int kv_heads, int dim, int vdim, cudaStream_t st) {
+    if (tokens == 0) return B200_OK;
+    const DeltaRow lay = delta_row(heads, kv_heads, dim, vdim);
+    const size_t smem = ((size_t)2 * kv_heads * dim + heads * vdim) * sizeof(float);
+    B200_DISPATCH_DTYPE(dtype, {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_direct_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        delta_prep_direct_kernel<T><<<tokens, tokens <= 64 ? 1024 : 256, smem, st>>>((const T *)proj, ld, col0, conv_w, taps, conv_state, decay_bias, a_log, rec,
+                                                                                   lay, tok_seq, tok_pos, seq_pos0, seq_slot, heads, kv_heads, dim, vdim);
+    });
+    return cuda_status("delta_prep_direct launch");
+}
+
+int launch_ssd_prep(int dtype, const void *proj, int ld, int col0, const float *conv_w, const float *conv_b, int taps, float *conv_state,
+                    const float *dt_bias, const float *a_log, const float *skip_w, float *rec, const int *tok_seq, const int *tok_pos,
+                    const int *seq_pos0, const int *seq_slot, int tokens, int heads, int groups, int state, int vdim, cudaStream_t st) {
+    if (tokens == 0) return B200_OK;
+    const DecayRow lay = decay_row(heads, groups, state, vdim);
+    B200_DISPATCH_DTYPE(dtype, {
+        ssd_prep_kernel<T><<<tokens, tokens <= 64 ? 1024 : 256, (size_t)heads * sizeof(float), st>>>((const T *)proj, ld, col0, conv_w, conv_b, taps, conv_state, dt_bias,
+                                                                                                   a_log, skip_w, rec, lay, tok_seq, tok_pos, seq_pos0, seq_slot,
+                                                                                                   heads, groups, state, vdim);
+    });
+    return cuda_status("ssd_prep launch");
+}
+
+int launch_linear_prep(int dtype, const void *proj, int ld, int col0, const float *head_decay, float *rec, int tokens, int heads, int dim, int vdim,
+                       cudaStream_t st) {
+    if (tokens == 0) return B200_OK;
+    const DecayRow lay = decay_row(heads, heads, dim, vdim);
+    B200_DISPATCH_DTYPE(dtype, { linear_prep_kernel<T><<<tokens, 256, 0, st>>>((const T *)proj, ld, col0, head_decay, rec, lay, heads, dim, vdim); });
+    return cuda_status("linear_prep launch");
+}
+
+int launch_decay_recurrent(const float *rec, float *S, float *o, const int *seq_start, const int *seq_pos0, const int *seq_slot, int n_seqs,
+                           int heads, int kv_heads, int dim, int vdim, cudaStream_t st, int one_token) {
+    const DecayRow lay = decay_row(heads, kv_heads, dim, vdim);
+    return launch_colrec<2>(rec, lay.ld, lay.q, lay.k, lay.v, lay.decay, lay.decay, S, nullptr, nullptr, o, nullptr, nullptr, seq_start, seq_pos0,
+                            seq_slot, n_seqs, heads, kv_heads, dim, vdim, one_token, st);
+}
+
+int launch_group_output(int dtype, const float *o, const float *skip, int skip_ld, const float *w, float eps, const void *gate, int gate_ld,
+                        int gate_act, int gate_first, void *out, int out_ld, int tokens, int cols, int groups, cudaStream_t st) {
+    if (tokens == 0) return B200_OK;
+    const int per = cols / groups, threads = per <= 64 ? 32 : (per <= 256 ? 64 : (per <= 1024 ? 128 : 256));
+    B200_DISPATCH_DTYPE(dtype, {
+        group_output_kernel<T><<<tokens * groups, threads, 0, st>>>(o, skip, skip_ld, w, eps, (const T *)gate, gate_ld, gate_act, gate_first, (T *)out, out_ld,
+                                                                   cols, groups);
+    });
+    return cuda_status("group_output launch");
 }
 
 }  // namespace b200

@@ -16,9 +16,10 @@ class HybridDecoder:
     The tensors are kept alive by this object."""
 
     def __init__(self, width, vocab, eps, layers, embedding, final_norm, lm_head, dtype, device, max_tokens, max_seqs, max_pages_per_seq,
-                 embed_scale=1.0, logit_softcap=0.0, final_norm_kind=0, loop=None):
-        """loop: None, or dict(start, stop, times, w_entry [width, 2*width] of the engine dtype, step fp32 [times, width]): the layers
-        start .. stop-1 run `times` times with the same weights, every pass behind the entry step x <- w_entry [x ; x0] + step[pass]."""
+                 embed_scale=1.0, logit_softcap=0.0, final_norm_kind=0, loop=None, logit_scale=1.0, streams=0):
+        """loop: None, or dict(start, stop, times[, w_entry [width, 2*width] of the engine dtype, step fp32 [times, width]]): the layers
+        start .. stop-1 run `times` times with the same weights; shared-norm layers open every pass with the entry step
+        x <- w_entry [x ; x0] + step[pass].  streams: residual streams of pre-norm layers (0: one)."""
         import torch
 
         m = _mod()
@@ -27,19 +28,23 @@ class HybridDecoder:
         code = {torch.float32: m.F32, torch.float16: m.F16, torch.bfloat16: m.BF16}[dtype]
         self.cfg = m.HybridConfig(int(width), int(vocab), len(layers), code, float(eps), int(max_tokens), int(max_seqs), int(max_pages_per_seq),
                                   float(embed_scale), float(logit_softcap), int(final_norm_kind),
-                                  int(loop["start"]) if loop else 0, int(loop["stop"]) if loop else 0, int(loop["times"]) if loop else 0)
+                                  int(loop["start"]) if loop else 0, int(loop["stop"]) if loop else 0, int(loop["times"]) if loop else 0,
+                                  float(logit_scale), int(streams))
         self.handle = m.lib().b200_hybrid_create(C.byref(self.cfg))
         if not self.handle:
             raise m.B200Error(m.lib().b200_last_error_string().decode())
         self._keep = [layers, embedding, final_norm, lm_head, loop]
         self.layers = layers
         ints = ("mixer", "heads", "kv_heads", "dim", "vdim", "chunk", "decay_rank", "mlp", "experts", "top", "expert_ff", "shared_ff", "act",
-                "norm", "window", "kv_rank", "rot_dim", "rot_dims", "route", "identity", "gated", "attn_weight", "out_gate", "conv", "gate_rank")
+                "norm", "window", "kv_rank", "rot_dim", "rot_dims", "route", "identity", "gated", "attn_weight", "out_gate", "conv", "gate_rank",
+                "rot_half", "v_norm", "gate_act", "norm_groups")
         tensors = ("w_in", "w_out", "q_norm", "k_norm", "sink", "w_decay", "decay_bias", "out_norm", "norm1", "norm2", "w_router", "w_up",
                    "w_down", "w_shared_up", "w_shared_down", "kv_norm", "w_uk_t", "w_uv", "pre1", "post1", "pre2", "post2", "ls1", "ls2",
-                   "route_bias", "b_up", "b_down", "head_bias", "dist_r1", "dist_r2", "b_in", "b_out", "conv_w", "a_log", "w_gate2")
+                   "route_bias", "b_up", "b_down", "head_bias", "dist_r1", "dist_r2", "b_in", "b_out", "conv_w", "a_log", "w_gate2", "conv_b", "skip",
+                   "head_decay", "hc1", "hc2", "branch_norm")
         f32_vectors = {"q_norm", "k_norm", "sink", "decay_bias", "out_norm", "norm1", "norm2", "kv_norm", "pre1", "post1", "pre2", "post2",
-                       "ls1", "ls2", "route_bias", "b_up", "b_down", "head_bias", "dist_r1", "dist_r2", "b_in", "b_out", "conv_w", "a_log"}
+                       "ls1", "ls2", "route_bias", "b_up", "b_down", "head_bias", "dist_r1", "dist_r2", "b_in", "b_out", "conv_w", "a_log", "conv_b", "skip",
+                       "head_decay", "hc1", "hc2", "branch_norm"}
 
         def fill(spec, where):
             lw = m.HybridLayer()
@@ -48,6 +53,8 @@ class HybridDecoder:
             lw.scale, lw.tau = float(spec.get("scale", 1.0)), float(spec.get("tau", 1.0))
             lw.rot_base, lw.kv_from = float(spec.get("rot_base", 0.0)), int(spec.get("kv_from", -1))
             lw.gate_cap, lw.mix_scale, lw.side_scale = float(spec.get("gate_cap", 0.0)), float(spec.get("mix_scale", 1.0)), float(spec.get("side_scale", 1.0))
+            for k in ("rot_factor", "rot_low", "rot_high", "rot_original", "softcap"):
+                setattr(lw, k, float(spec.get(k, 0.0)))
             for k in tensors:
                 t = spec.get(k)
                 if t is not None:
@@ -62,7 +69,7 @@ class HybridDecoder:
                 side = fill(spec["side"], f"layer {i} (second mixer)")
                 lw.side = C.addressof(side)
             m.check(m.lib().b200_hybrid_set_layer(self.handle, i, C.byref(lw)))
-        if loop:
+        if loop and loop.get("w_entry") is not None:
             assert loop["w_entry"].dtype == dtype and loop["w_entry"].is_contiguous() and loop["step"].dtype == torch.float32 and loop["step"].is_contiguous()
             m.check(m.lib().b200_hybrid_set_loop(self.handle, m.ptr(loop["w_entry"]), m.ptr(loop["step"])))
         self.num_runs = m.lib().b200_hybrid_num_runs(self.handle)

@@ -26,7 +26,7 @@ def architectures():
 
 
 def _populate():
-    for sub in ("vasolix", "zefenex", "fedovik", "llama"):
+    for sub in ("vasolix", "zefenex", "fedovik", "silonex", "llama"):
         importlib.import_module(f"{__name__}.{sub}")
 
 
