@@ -846,6 +846,10 @@ SHARED_NORM_SIZES = {  # Fedovik-shaped layer lists (attention, parallel, mlstm,
 
 
 def run_fedovik(args):
+    print(json.dumps(fedovik_result(args)), flush=True)
+
+
+def fedovik_result(args):
     """--mode fedovik: prefill and decode throughput of a Fedovik-shaped model (random weights, bf16) on the layer-list decoder at one of
     SHARED_NORM_SIZES, and, in the same process, of the framework's closest other design at equal width: the Vasolix-shaped model of --mode
     hybrid (attention and gated-linear-attention layers).  Prefill: one prompt of --prefill-tokens tokens in one engine call.  Decode:
@@ -963,7 +967,7 @@ def run_fedovik(args):
     kv_bytes = es * B * (n_att * A["kv_heads"] * (A["dim"] + A["vdim"]) * (ctx + 1) + n_par * L["kv_heads"] * (L["dim"] + L["vdim"]) * min(ctx + 1, L["window"]))
     st_bytes = 2 * 4 * B * (n_par * R["heads"] * R["dim"] * R["vdim"] + M["heads"] * M["dim"] * M["vdim"])
     dec_gbs = (w_bytes + kv_bytes + st_bytes) / (dec_ms * 1e-3) / 1e9
-    print(json.dumps({
+    return ({
         "metric": "shared-norm model prefill / decode tokens/s", "value": Tq * 1e3 / pre_ms, "unit": "tokens/s (prefill)", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "b200",
         "config": {"model": f"Fedovik-shaped, size {args.fedovik_size}: width {W}, layers attention / parallel / mlstm / parallel, the first two twice "
@@ -975,6 +979,155 @@ def run_fedovik(args):
                                "frac_of_measured_hbm": dec_gbs / float(peaks.get("hbm_gbs", 6650.0)), "clocks": dec_clocks}},
         "closest": None if args.no_closest else {k: v for k, v in hybrid_result(argparse.Namespace(**dict(vars(args), hybrid_size=args.fedovik_size))).items()
                                                  if k in ("config", "prefill", "decode")},
+        "e2e": "both numbers are taken through HybridDecoder.forward: host batch description in (one H2D copy per call), device logits out"})
+
+
+STREAM_SIZES = {  # Silonex-shaped layer lists (lightning, mamba2, parallel, parallel; the second and third layer run twice: six layer runs), four
+    # residual streams, random weights.  Widths, feed-forwards and the parallel layer follow SHARED_NORM_SIZES, so that the Fedovik-shaped model
+    # of the same numbers stands beside it.
+    "s": dict(width=1024, ff=2816, light=dict(heads=8, dim=128, vdim=128), ssd=dict(heads=32, vdim=64, state=128, groups=4, norm_groups=4),
+              left=dict(heads=8, kv_heads=2, dim=128, vdim=128, window=512), right=dict(heads=4, kv_heads=4, dim=64, vdim=256)),
+    "m": dict(width=2048, ff=5632, light=dict(heads=16, dim=128, vdim=128), ssd=dict(heads=64, vdim=64, state=128, groups=8, norm_groups=8),
+              left=dict(heads=16, kv_heads=4, dim=128, vdim=128, window=1024), right=dict(heads=8, kv_heads=8, dim=128, vdim=256)),
+    "l": dict(width=4096, ff=11008, light=dict(heads=32, dim=128, vdim=128), ssd=dict(heads=128, vdim=64, state=128, groups=8, norm_groups=8),
+              left=dict(heads=32, kv_heads=8, dim=128, vdim=128, window=2048), right=dict(heads=16, kv_heads=16, dim=128, vdim=256)),
+}
+
+
+def run_silonex(args):
+    """--mode silonex: prefill and decode throughput of a Silonex-shaped model (random weights, bf16) on the layer-list decoder at one of
+    STREAM_SIZES, and, in the same process, of the framework's closest other design at equal width: the Fedovik-shaped model of --mode
+    fedovik (windowed attention beside a delta rule, recurrent layers, a looped block).  Prefill: one prompt of --prefill-tokens tokens in
+    one engine call.  Decode: --batch sequences with --ctx cached positions each, one token per sequence per step."""
+    import numpy as np
+    import torch
+
+    mod = importlib.import_module("llm-inference-engine_b200")
+    mod.lib()
+    sil = importlib.import_module("llm-inference-engine_b200.models.silonex")
+    sz = STREAM_SIZES[args.silonex_size]
+    W, FF, LI, SS, L, R, V, NS = sz["width"], sz["ff"], sz["light"], sz["ssd"], sz["left"], sz["right"], 32000, 4
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    mlp = {"kind": "dense", "ff": FF}
+    lig = {"type": "lightning", "mixer": dict(heads=LI["heads"], dim=LI["dim"], vdim=LI["vdim"],
+                                              decay=[1.0 - 2.0 ** (-5 - 5 * h / max(LI["heads"] - 1, 1)) for h in range(LI["heads"])]), "mlp": mlp}
+    ssd = {"type": "mamba2", "mixer": dict(heads=SS["heads"], vdim=SS["vdim"], state=SS["state"], groups=SS["groups"], conv=4, norm_groups=SS["norm_groups"]),
+           "mlp": mlp}
+    par = {"type": "parallel", "mixer": dict(left=dict(heads=L["heads"], kv_heads=L["kv_heads"], dim=L["dim"], vdim=L["vdim"], scale=L["dim"] ** -0.5,
+                                                       softcap=50.0, mask=dict(size=L["window"]),
+                                                       rot=dict(base=5e5, dims=L["dim"], scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192))),
+                                             right=dict(heads=R["heads"], kv_heads=R["kv_heads"], dim=R["dim"], vdim=R["vdim"], conv=4)), "mlp": mlp}
+    config = {"architecture": "Silonex", "layers": [lig, ssd, par, par], "loop": {"start": 1, "stop": 3, "times": 2}, "norm": {"eps": 1e-5},
+              "streams": NS, "logit_scale": 0.5, "vocab": V, "width": W}
+    runs = [0, 1, 2, 1, 2, 3]
+    gen = torch.Generator().manual_seed(7)
+
+    def rnd(*shape, std=0.02):
+        return (torch.randn(*shape, generator=gen) * std).to(torch.bfloat16)
+
+    def ones(n):
+        return torch.ones(n, dtype=torch.bfloat16)
+
+    t = {"embed": rnd(V, W, std=0.5), "final.norm": ones(W), "final.norm.b": rnd(W)}
+    for i, layer in enumerate(config["layers"]):
+        p, mx = f"l{i}.", layer["mixer"]
+        for q in ("1", "2"):
+            t[p + "norm" + q], t[p + "norm" + q + ".b"] = ones(W), rnd(W)
+            t[p + f"hc{q}.in"], t[p + f"hc{q}.out"] = torch.full((NS,), 1.0 / NS).to(torch.bfloat16), ones(NS)
+            t[p + f"hc{q}.mix"] = (torch.eye(NS) + 0.05 * torch.randn(NS, NS, generator=gen)).to(torch.bfloat16)
+        t.update({p + "mlp.gate": rnd(FF, W), p + "mlp.up": rnd(FF, W), p + "mlp.down": rnd(W, FF)})
+        pre = p + "mix."
+        if layer["type"] == "lightning":
+            H, dk, dv = mx["heads"], mx["dim"], mx["vdim"]
+            t.update({pre + "q": rnd(H * dk, W), pre + "k": rnd(H * dk, W), pre + "v": rnd(H * dv, W), pre + "g": rnd(H * dv, W), pre + "o": rnd(W, H * dv),
+                      pre + "norm": ones(H * dv)})
+        elif layer["type"] == "mamba2":
+            H, P, N, G = mx["heads"], mx["vdim"], mx["state"], mx["groups"]
+            t.update({pre + "in": rnd(2 * H * P + 2 * G * N + H, W), pre + "conv": rnd(H * P + 2 * G * N, 4, std=0.5), pre + "conv.b": rnd(H * P + 2 * G * N),
+                      pre + "dt_bias": rnd(H, std=1.0), pre + "A_log": torch.zeros(H, dtype=torch.bfloat16), pre + "D": ones(H), pre + "norm": ones(H * P),
+                      pre + "o": rnd(W, H * P)})
+        else:
+            H, G, dk, dv = L["heads"], L["kv_heads"], L["dim"], L["vdim"]
+            lp = pre + "left."
+            t.update({lp + "q": rnd(H * dk, W), lp + "k": rnd(G * dk, W), lp + "v": rnd(G * dv, W), lp + "o": rnd(W, H * dv), lp + "q.norm": ones(dk),
+                      lp + "k.norm": ones(dk), pre + "left.out": ones(W), pre + "right.out": ones(W)})
+            rp, H, G, dk, dv = pre + "right.", R["heads"], R["kv_heads"], R["dim"], R["vdim"]
+            t.update({rp + "q": rnd(G * dk, W), rp + "k": rnd(G * dk, W), rp + "v": rnd(H * dv, W), rp + "b": rnd(H, W), rp + "a": rnd(H, W), rp + "g": rnd(H * dv, W),
+                      rp + "o": rnd(W, H * dv), rp + "q.conv": rnd(G * dk, 4, std=0.5), rp + "k.conv": rnd(G * dk, 4, std=0.5),
+                      rp + "v.conv": rnd(H * dv, 4, std=0.5), rp + "dt_bias": rnd(H, std=1.0), rp + "A_log": torch.zeros(H, dtype=torch.bfloat16),
+                      rp + "norm": ones(dv)})
+    Tq, B, ctx = args.prefill_tokens, args.batch, args.ctx
+    page = mod.KV_PAGE_SIZE
+    per_seq = (max(Tq, ctx + args.steps + args.warmup + 8) + page - 1) // page
+    model = sil.SilonexModel(config, t, dtype="bfloat16", device=dev, max_tokens=max(Tq, B, 2048), max_seqs=max(B, 1), max_pages_per_seq=per_seq)
+    eng = model.engine
+    eng.set_pools(per_seq * max(B, 1), max(B, 1))
+    ids = torch.randint(0, V, (max(Tq, ctx + 1),), generator=gen).tolist()
+    bt = np.arange(per_seq * max(B, 1), dtype=np.int32).reshape(max(B, 1), per_seq)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    # matrix parameters a token passes, per layer (the looped layers count twice)
+    lig_p = W * (2 * LI["heads"] * LI["dim"] + 3 * LI["heads"] * LI["vdim"])
+    ssd_p = W * (3 * SS["heads"] * SS["vdim"] + 2 * SS["groups"] * SS["state"] + SS["heads"])
+    left_p = W * ((L["heads"] + L["kv_heads"]) * L["dim"] + L["kv_heads"] * L["vdim"] + L["heads"] * L["vdim"])
+    right_p = W * (2 * R["kv_heads"] * R["dim"] + 3 * R["heads"] * R["vdim"] + 2 * R["heads"])
+    layer_p = [lig_p + 3 * W * FF, ssd_p + 3 * W * FF, left_p + right_p + 3 * W * FF, left_p + right_p + 3 * W * FF]
+    active = sum(layer_p[i] for i in runs)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(0, gpu_uuid(dev)) as clocks:
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps, clocks.summary()
+
+    pre_ms, pre_clocks = timed(lambda: eng.forward(ids[:Tq], [0, Tq], [0], [0], bt[:1].reshape(-1), [Tq - 1]), max(3, min(args.steps, 20)), 3)
+    n_lig, n_ssd, n_par = runs.count(0), runs.count(1), runs.count(2) + runs.count(3)
+    attn_flops = n_par * 2.0 * L["heads"] * (L["dim"] + L["vdim"]) * sum(min(i + 1, L["window"]) for i in range(Tq))
+    lig_state, ssd_state, del_state = LI["heads"] * LI["dim"] * LI["vdim"], SS["heads"] * SS["state"] * SS["vdim"], R["heads"] * R["dim"] * R["vdim"]
+    rec_flops = (n_lig * 2 * 2.0 * lig_state + n_ssd * 2 * 2.0 * ssd_state + n_par * 2 * 3.0 * del_state) * Tq
+    pre_tflops = (2.0 * Tq * active + attn_flops + rec_flops) / (pre_ms * 1e-3) / 1e12
+    for b in range(B):
+        eng.forward(ids[:ctx], [0, ctx], [0], [b], bt[b:b + 1].reshape(-1), [])
+    state = {"pos": ctx}
+
+    def step():
+        eng.forward(ids[:B], list(range(B + 1)), [state["pos"]] * B, list(range(B)), bt.reshape(-1), list(range(B)))
+        state["pos"] += 1
+
+    dec_ms, dec_clocks = timed(step, args.steps, max(args.warmup, 3))
+    es = 2
+    w_bytes = es * active + es * V * W
+    kv_bytes = es * B * n_par * L["kv_heads"] * (L["dim"] + L["vdim"]) * min(ctx + 1, L["window"])
+    st_bytes = 2 * 4 * B * (n_lig * lig_state + n_ssd * ssd_state + n_par * del_state)
+    dec_gbs = (w_bytes + kv_bytes + st_bytes) / (dec_ms * 1e-3) / 1e9
+    closest = None
+    if not args.no_closest:
+        del model, eng
+        torch.cuda.empty_cache()
+        near = fedovik_result(argparse.Namespace(**dict(vars(args), fedovik_size=args.silonex_size, no_closest=True)))
+        closest = {"config": near["config"], "prefill": near["fedovik"]["prefill"], "decode": near["fedovik"]["decode"]}
+    print(json.dumps({
+        "metric": "stream model prefill / decode tokens/s", "value": Tq * 1e3 / pre_ms, "unit": "tokens/s (prefill)", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "b200",
+        "config": {"model": f"Silonex-shaped, size {args.silonex_size}: width {W}, {NS} residual streams, layers lightning / mamba2 / parallel / parallel, "
+                            f"the second and third twice (6 layer runs), ff {FF}, window {L['window']}", "prefill_tokens": Tq, "decode_batch": B,
+                   "decode_context": ctx, "cache_policy": "weights larger than L2 at sizes m and l; no explicit flush"},
+        "silonex": {"prefill": {"tokens_per_s": Tq * 1e3 / pre_ms, "ms": pre_ms, "tflops": pre_tflops,
+                                "frac_of_measured_bf16_sustained": pre_tflops / float(peaks.get("bf16_tflops_sustained", 1400.0)), "clocks": pre_clocks},
+                    "decode": {"tokens_per_s": B * 1e3 / dec_ms, "ms_per_step": dec_ms, "algorithmic_gb_per_s": dec_gbs,
+                               "frac_of_measured_hbm": dec_gbs / float(peaks.get("hbm_gbs", 6650.0)), "clocks": dec_clocks}},
+        "closest": closest,
         "e2e": "both numbers are taken through HybridDecoder.forward: host batch description in (one H2D copy per call), device logits out"}), flush=True)
 
 
@@ -1163,8 +1316,9 @@ def main():
     ap.add_argument("--hybrid-size", default="m", choices=list(HYBRID_SIZES), help="--mode hybrid: which Vasolix-shaped model")
     ap.add_argument("--latent-size", default="m", choices=list(LATENT_SIZES), help="--mode latent: which Zefenex-shaped model")
     ap.add_argument("--fedovik-size", default="m", choices=list(SHARED_NORM_SIZES), help="--mode fedovik: which Fedovik-shaped model")
-    ap.add_argument("--no-closest", action="store_true", help="--mode fedovik: leave out the Vasolix-shaped model beside it")
-    ap.add_argument("--mode", default="decode", choices=["decode", "prefill", "generate", "serve", "hybrid", "latent", "fedovik"],
+    ap.add_argument("--silonex-size", default="m", choices=list(STREAM_SIZES), help="--mode silonex: which Silonex-shaped model")
+    ap.add_argument("--no-closest", action="store_true", help="--mode fedovik / silonex: leave out the closest other model beside it")
+    ap.add_argument("--mode", default="decode", choices=["decode", "prefill", "generate", "serve", "hybrid", "latent", "fedovik", "silonex"],
                     help="decode (default, the BASELINE metric); prefill: one pass of --prefill-tokens tokens through all layers; generate: "
                          "the whole loop through b200_generate (prompt of --prefill-tokens tokens, --new-tokens sampled tokens, host in / host out)")
     ap.add_argument("--new-tokens", type=int, default=128)
@@ -1196,6 +1350,9 @@ def main():
         return
     if args.mode == "latent":
         run_latent(args)
+        return
+    if args.mode == "silonex":
+        run_silonex(args)
         return
     if args.mode == "fedovik":
         run_fedovik(args)

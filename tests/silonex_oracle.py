@@ -242,6 +242,43 @@ def forward(config, W, tokens, trace=False):
     return (logits, torch.stack(after)) if trace else logits
 
 
+# ---- small configurations for the tests
+def dense(ff=48):
+    return {"kind": "dense", "ff": ff}
+
+
+def lightning_layer(heads=2, dim=8, vdim=12, decay=None, mlp=None):
+    decay = decay if decay is not None else [0.5 + 0.49 * (h + 1) / heads for h in range(heads)]
+    return {"type": "lightning", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": decay}, "mlp": mlp}
+
+
+def mamba_layer(heads=4, vdim=6, state=10, groups=2, conv=3, norm_groups=3, mlp=None):
+    return {"type": "mamba2", "mixer": {"heads": heads, "vdim": vdim, "state": state, "groups": groups, "conv": conv, "norm_groups": norm_groups},
+            "mlp": mlp}
+
+
+def pair_layer(heads=4, kv_heads=2, dim=16, vdim=12, window=30, rot_dims=8, base=100.0, scaling=True, scale=0.3, softcap=6.0, r_heads=4,
+               r_kv_heads=2, r_dim=8, r_vdim=10, conv=3, mlp=None):
+    rot = {"base": base, "dims": rot_dims}
+    if scaling:   # wavelengths of base 100 over 8 dims: 6, 20, 63, 199: one stays, two are blended, one is slowed down
+        rot["scaling"] = scaling if isinstance(scaling, dict) else {"factor": 4.0, "low": 1.0, "high": 8.0, "original": 128}
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": window}, "rot": rot, "scale": scale, "softcap": softcap}
+    right = {"heads": r_heads, "kv_heads": r_kv_heads, "dim": r_dim, "vdim": r_vdim, "conv": conv}
+    return {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp}
+
+
+def make_config(layers, width=32, vocab=50, streams=3, loop=None, logit_scale=0.5, eps=1e-5):
+    import copy
+
+    config = {"architecture": "Silonex", "layers": copy.deepcopy(layers), "norm": {"eps": eps}, "vocab": vocab, "width": width,
+              "logit_scale": logit_scale}
+    if streams:
+        config["streams"] = streams
+    if loop:
+        config["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return config
+
+
 def random_model(config, seed=0):
     """Random tensors with the checkpoint's names, rounded to bfloat16 (returned both as float64 for the oracle and packed for the engine)."""
     gen = torch.Generator().manual_seed(seed)
