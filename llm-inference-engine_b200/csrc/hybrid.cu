@@ -557,82 +557,143 @@ final_ln_rows_kernel(const float *__restrict__ x, const int *__restrict__ rows, 
 //   h_out[t, :] = T(layernorm(sum_v in_next[v] * xs[t, v]; ln_next))              (hc_next packed alike; NULL: the one stream itself).
 // Everything is fp32; the row waits in shared memory between the passes (mean first, then the squared deviations).
 constexpr int kMaxStreams = 8;
-template <typename T>
+// N (1 or 4) consecutive elements of T <-> fp32; N == 4: one 16-byte (fp32) or 8-byte (16-bit) access, the address aligned to it
+template <typename T, int N> __device__ __forceinline__ void load_n(const T *__restrict__ p, float *v) {
+    if constexpr (N == 1) {
+        v[0] = Elem<T>::to_f(p[0]);
+    } else if constexpr (sizeof(T) == 4) {
+        const float4 a = *reinterpret_cast<const float4 *>(p);
+        v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
+    } else {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+        const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = Elem<T>::to_f(e[i]);
+    }
+}
+template <typename T, int N> __device__ __forceinline__ void store_n(T *__restrict__ p, const float *v) {
+    if constexpr (N == 1) {
+        p[0] = Elem<T>::from_f(v[0]);
+    } else if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        uint2 raw;
+        T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) e[i] = Elem<T>::from_f(v[i]);
+        *reinterpret_cast<uint2 *>(p) = raw;
+    }
+}
+// SC: the stream count at compile time (0: any count up to kMaxStreams, given as S).  VEC: four columns per access.  The coefficients live
+// in registers; a thread's loads of one piece (all streams and both rows) are independent of one another and in flight together.
+template <typename T, int SC, bool VEC>
 __global__ void __launch_bounds__(256)
-stream_residual_kernel(float *__restrict__ xs, int S, const float *__restrict__ x_init, const T *__restrict__ ya, const T *__restrict__ yb,
+stream_residual_kernel(float *xs, int S_any, const float *__restrict__ x_init, const T *__restrict__ ya, const T *__restrict__ yb,
                        const float *__restrict__ na, const float *__restrict__ nb, float sa, float sb, const float *__restrict__ hc,
                        const float *__restrict__ hc_next, const float *__restrict__ ln_next, float eps, int width, T *__restrict__ h_out,
                        float *__restrict__ sum_out, float *__restrict__ trace) {
     extern __shared__ __align__(16) float row[];  // [width]
     __shared__ float red[33];
-    __shared__ float c_out[kMaxStreams], c_in[kMaxStreams], c_mix[kMaxStreams * kMaxStreams];
+    constexpr int N = VEC ? 4 : 1, SM = SC > 0 ? SC : kMaxStreams;
+    const int S = SC > 0 ? SC : S_any;
     const int t = blockIdx.x;
-    if (threadIdx.x < S) {
-        c_out[threadIdx.x] = hc ? hc[S + threadIdx.x] : 1.0f;
-        c_in[threadIdx.x] = hc_next ? hc_next[threadIdx.x] : 1.0f;
+    float c_out[SM], c_in[SM], c_mix[SM][SM];  // c_mix[from][to]
+#pragma unroll
+    for (int v = 0; v < SM; ++v) {
+        c_out[v] = (v < S && hc) ? hc[S + v] : 1.0f;
+        c_in[v] = (v < S && hc_next) ? hc_next[v] : 1.0f;
+#pragma unroll
+        for (int q = 0; q < SM; ++q) c_mix[q][v] = (v < S && q < S && hc) ? hc[2 * S + q * S + v] : (q == v ? 1.0f : 0.0f);
     }
-    if (threadIdx.x < S * S) c_mix[threadIdx.x] = hc ? hc[2 * S + threadIdx.x] : (threadIdx.x / S == threadIdx.x % S ? 1.0f : 0.0f);
+    const T *yar = ya + (size_t)t * width, *ybr = yb + (size_t)t * width;
     float ia = 1.0f, ib = 1.0f;
     if (ya && na) {  // (uniform over the CTA)
         float ssa = 0.0f, ssb = 0.0f;
-        for (int c = threadIdx.x; c < width; c += blockDim.x) {
-            const float a = Elem<T>::to_f(ya[(size_t)t * width + c]);
-            ssa = fmaf(a, a, ssa);
+        for (int c = threadIdx.x * N; c < width; c += blockDim.x * N) {
+            float a[N], b[N];
+            load_n<T, N>(yar + c, a);
+#pragma unroll
+            for (int i = 0; i < N; ++i) ssa = fmaf(a[i], a[i], ssa);
             if (yb) {
-                const float b = Elem<T>::to_f(yb[(size_t)t * width + c]);
-                ssb = fmaf(b, b, ssb);
+                load_n<T, N>(ybr + c, b);
+#pragma unroll
+                for (int i = 0; i < N; ++i) ssb = fmaf(b[i], b[i], ssb);
             }
         }
         ia = sa * rsqrtf(block_sum(ssa, red) / (float)width + eps);
         if (yb) ib = sb * rsqrtf(block_sum(ssb, red) / (float)width + eps);
     }
-    __syncthreads();
     float sum = 0.0f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float y = 0.0f;
+    for (int c = threadIdx.x * N; c < width; c += blockDim.x * N) {
+        float y[N], old[SM][N];
+#pragma unroll
+        for (int v = 0; v < SM; ++v)
+            if (v < S) load_n<float, N>(x_init ? x_init + (size_t)t * width + c : xs + ((size_t)t * S + v) * width + c, old[v]);
+#pragma unroll
+        for (int i = 0; i < N; ++i) y[i] = 0.0f;
         if (ya) {
-            y = Elem<T>::to_f(ya[(size_t)t * width + c]);
+            load_n<T, N>(yar + c, y);
             if (na) {
-                y *= ia * na[c];
-                if (yb) y = fmaf(Elem<T>::to_f(yb[(size_t)t * width + c]) * ib, nb[c], y);
+                float w[N];
+                load_n<float, N>(na + c, w);
+#pragma unroll
+                for (int i = 0; i < N; ++i) y[i] *= ia * w[i];
+                if (yb) {
+                    float b[N];
+                    load_n<T, N>(ybr + c, b);
+                    load_n<float, N>(nb + c, w);
+#pragma unroll
+                    for (int i = 0; i < N; ++i) y[i] = fmaf(b[i] * ib, w[i], y[i]);
+                }
             }
         }
-        float old[kMaxStreams];
+        float u[N], total[N];
 #pragma unroll
-        for (int v = 0; v < kMaxStreams; ++v)
-            if (v < S) old[v] = x_init ? x_init[(size_t)t * width + c] : xs[((size_t)t * S + v) * width + c];
-        float u = 0.0f, total = 0.0f;
+        for (int i = 0; i < N; ++i) u[i] = total[i] = 0.0f;
 #pragma unroll
-        for (int v = 0; v < kMaxStreams; ++v) {
-            if (v >= S) break;
-            float a;
-            if (x_init) {
-                a = old[v];
-            } else {
-                a = c_out[v] * y;
+        for (int v = 0; v < SM; ++v) {
+            if (v < S) {
+                float a[N];
 #pragma unroll
-                for (int q = 0; q < kMaxStreams; ++q)
-                    if (q < S) a = fmaf(c_mix[q * S + v], old[q], a);
+                for (int i = 0; i < N; ++i) {
+                    if (x_init) {
+                        a[i] = old[v][i];
+                    } else {
+                        a[i] = c_out[v] * y[i];
+#pragma unroll
+                        for (int q = 0; q < SM; ++q)
+                            if (q < S) a[i] = fmaf(c_mix[q][v], old[q][i], a[i]);
+                    }
+                    total[i] += a[i];
+                    u[i] = fmaf(c_in[v], a[i], u[i]);
+                }
+                if (x_init || ya) store_n<float, N>(xs + ((size_t)t * S + v) * width + c, a);
             }
-            if (x_init || ya) xs[((size_t)t * S + v) * width + c] = a;
-            total += a;
-            u = fmaf(c_in[v], a, u);
         }
-        if (trace) trace[(size_t)t * width + c] = total;
-        if (sum_out) sum_out[(size_t)t * width + c] = total;
-        row[c] = u;
-        sum += u;
+        if (trace) store_n<float, N>(trace + (size_t)t * width + c, total);
+        if (sum_out) store_n<float, N>(sum_out + (size_t)t * width + c, total);
+#pragma unroll
+        for (int i = 0; i < N; ++i) row[c + i] = u[i], sum += u[i];
     }
     if (!h_out) return;
     const float mean = block_sum(sum, red) / (float)width;
     float sq = 0.0f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        const float dv = row[c] - mean;
-        sq = fmaf(dv, dv, sq);
+    for (int c = threadIdx.x * N; c < width; c += blockDim.x * N) {  // (a thread reads back the pieces of row[] it wrote)
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+            const float dv = row[c + i] - mean;
+            sq = fmaf(dv, dv, sq);
+        }
     }
     const float inv = rsqrtf(block_sum(sq, red) / (float)width + eps);
-    for (int c = threadIdx.x; c < width; c += blockDim.x)
-        h_out[(size_t)t * width + c] = Elem<T>::from_f(fmaf((row[c] - mean) * inv, ln_next[c], ln_next[width + c]));
+    for (int c = threadIdx.x * N; c < width; c += blockDim.x * N) {
+        float w[N], b[N], o[N];
+        load_n<float, N>(ln_next + c, w);
+        load_n<float, N>(ln_next + width + c, b);
+#pragma unroll
+        for (int i = 0; i < N; ++i) o[i] = fmaf((row[c + i] - mean) * inv, w[i], b[i]);
+        store_n<T, N>(h_out + (size_t)t * width + c, o);
+    }
 }
 
 // where one mixer of one layer run keeps what it remembers
@@ -1299,10 +1360,23 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
     // the residual step of one sublayer + the layer-normed input of the sublayer that follows (hc_next / ln_next; none after the last run)
     auto stream_step = [&](const float *x_init, const void *ya, const void *yb, const float *na, const float *nb, float sa, float sb, const float *hc,
                            const float *hc_next, const float *ln_next, float *sum_out, float *trace) -> int {
+        // four columns per access when every row starts on a 16-byte boundary (the scratch buffers do; norm vectors and the trace are the caller's)
+        const bool vec = width % 4 == 0 && ((reinterpret_cast<size_t>(na) | reinterpret_cast<size_t>(nb) | reinterpret_cast<size_t>(ln_next) |
+                                              reinterpret_cast<size_t>(trace)) & 15) == 0;
+#define B200_STREAMS(SC, V) stream_residual_kernel<T, SC, V><<<NT, 256, (size_t)width * sizeof(float), st>>>(                                           \
+    m->xs, n_streams, x_init, (const T *)ya, (const T *)yb, na, nb, sa, sb, hc, hc_next, ln_next, c.norm_eps, width, ln_next ? (T *)m->h : nullptr, sum_out, trace)
+#define B200_STREAMS_V(SC) do { if (vec) B200_STREAMS(SC, true); else B200_STREAMS(SC, false); } while (0)
         B200_DISPATCH_DTYPE(dt, {
-            stream_residual_kernel<T><<<NT, 256, (size_t)width * sizeof(float), st>>>(m->xs, n_streams, x_init, (const T *)ya, (const T *)yb, na, nb, sa, sb, hc,
-                                                                                    hc_next, ln_next, c.norm_eps, width, ln_next ? (T *)m->h : nullptr, sum_out, trace);
+            switch (n_streams) {
+                case 1: B200_STREAMS_V(1); break;
+                case 2: B200_STREAMS_V(2); break;
+                case 3: B200_STREAMS_V(3); break;
+                case 4: B200_STREAMS_V(4); break;
+                default: B200_STREAMS_V(0); break;
+            }
         });
+#undef B200_STREAMS_V
+#undef B200_STREAMS
         return cuda_status("stream_residual launch");
     };
     auto pre_norm_layer = [&](int run) -> int {
