@@ -340,6 +340,33 @@ __device__ __forceinline__ void tp_reduce_vec(const TpExchange &t, unsigned int 
     for (int j = 0; j < V; ++j) f[j] = poisoned ? __int_as_float(0x7fc00000) : f[j];
 }
 
+// N (1 or 4) consecutive elements of T <-> fp32; N == 4: one 16-byte (fp32) or 8-byte (16-bit) access, the address aligned to it
+template <typename T, int N> __device__ __forceinline__ void load_n(const T *__restrict__ p, float *v) {
+    if constexpr (N == 1) {
+        v[0] = Elem<T>::to_f(p[0]);
+    } else if constexpr (sizeof(T) == 4) {
+        const float4 a = *reinterpret_cast<const float4 *>(p);
+        v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
+    } else {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+        const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = Elem<T>::to_f(e[i]);
+    }
+}
+template <typename T, int N> __device__ __forceinline__ void store_n(T *__restrict__ p, const float *v) {
+    if constexpr (N == 1) {
+        p[0] = Elem<T>::from_f(v[0]);
+    } else if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        uint2 raw;
+        T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) e[i] = Elem<T>::from_f(v[i]);
+        *reinterpret_cast<uint2 *>(p) = raw;
+    }
+}
 // ------------------------------------------------------------------ activations (b200_act_t)
 __device__ __forceinline__ float act_apply(float v, int act) {
     if (act == B200_ACT_RELU2) {

@@ -557,33 +557,6 @@ final_ln_rows_kernel(const float *__restrict__ x, const int *__restrict__ rows, 
 //   h_out[t, :] = T(layernorm(sum_v in_next[v] * xs[t, v]; ln_next))              (hc_next packed alike; NULL: the one stream itself).
 // Everything is fp32; the row waits in shared memory between the passes (mean first, then the squared deviations).
 constexpr int kMaxStreams = 8;
-// N (1 or 4) consecutive elements of T <-> fp32; N == 4: one 16-byte (fp32) or 8-byte (16-bit) access, the address aligned to it
-template <typename T, int N> __device__ __forceinline__ void load_n(const T *__restrict__ p, float *v) {
-    if constexpr (N == 1) {
-        v[0] = Elem<T>::to_f(p[0]);
-    } else if constexpr (sizeof(T) == 4) {
-        const float4 a = *reinterpret_cast<const float4 *>(p);
-        v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
-    } else {
-        const uint2 raw = *reinterpret_cast<const uint2 *>(p);
-        const T *e = reinterpret_cast<const T *>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = Elem<T>::to_f(e[i]);
-    }
-}
-template <typename T, int N> __device__ __forceinline__ void store_n(T *__restrict__ p, const float *v) {
-    if constexpr (N == 1) {
-        p[0] = Elem<T>::from_f(v[0]);
-    } else if constexpr (sizeof(T) == 4) {
-        *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
-    } else {
-        uint2 raw;
-        T *e = reinterpret_cast<T *>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) e[i] = Elem<T>::from_f(v[i]);
-        *reinterpret_cast<uint2 *>(p) = raw;
-    }
-}
 // SC: the stream count at compile time (0: any count up to kMaxStreams, given as S).  VEC: four columns per access.  The coefficients live
 // in registers; a thread's loads of one piece (all streams and both rows) are independent of one another and in flight together.
 template <typename T, int SC, bool VEC>

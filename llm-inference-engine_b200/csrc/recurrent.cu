@@ -219,28 +219,78 @@ linear_prep_kernel(const T *__restrict__ proj, int ld, int col0, const float *__
 // One CTA per (token, group): the read-out of a whole token (or of one of `groups` equal parts of it) normed together.
 //   y_c = o[t, c] + skip[t * skip_ld + c];   gate_first: y_c *= act(gate_c);   out[t, c] = T(y_c * rsqrt(mean_c y^2 + eps) * w[c] * (gate_first
 //   ? 1 : act(gate_c))), act = silu (gate_act 1) or sigmoid (0); c runs over the group's columns of the row of `cols`.
-template <typename T>
+// VEC: four columns per access (every piece starts on a boundary of its access).  A thread's values stay in registers between the sum and
+// the scaling when the group is short enough (kKeep pieces per thread), else they are formed twice.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 group_output_kernel(const float *__restrict__ o, const float *__restrict__ skip, int skip_ld, const float *__restrict__ w, float eps,
                     const T *__restrict__ gate, int gate_ld, int gate_act, int gate_first, T *__restrict__ out, int out_ld, int cols, int groups) {
     __shared__ float red[33];
+    constexpr int N = VEC ? 4 : 1, kKeep = VEC ? 2 : 8;
     const int t = blockIdx.x / groups, g = blockIdx.x - t * groups, per = cols / groups, c0 = g * per;
     auto act = [&](float z) { return gate_act ? z * sigmoid_r(z) : sigmoid_r(z); };
-    auto value = [&](int c) {
-        float y = o[(size_t)t * cols + c] + (skip ? skip[(size_t)t * skip_ld + c] : 0.0f);
-        if (gate_first) y *= act(Elem<T>::to_f(gate[(size_t)t * gate_ld + c]));
-        return y;
+    auto value = [&](int c, float *y) {
+        load_n<float, N>(o + (size_t)t * cols + c, y);
+        if (skip) {
+            float sk[N];
+            load_n<float, N>(skip + (size_t)t * skip_ld + c, sk);
+#pragma unroll
+            for (int i = 0; i < N; ++i) y[i] += sk[i];
+        }
+        if (gate_first) {
+            float z[N];
+            load_n<T, N>(gate + (size_t)t * gate_ld + c, z);
+#pragma unroll
+            for (int i = 0; i < N; ++i) y[i] *= act(z[i]);
+        }
     };
+    auto finish = [&](int c, float *y, float inv) {
+        float wv[N];
+        load_n<float, N>(w + c, wv);
+#pragma unroll
+        for (int i = 0; i < N; ++i) y[i] *= inv * wv[i];
+        if (!gate_first) {
+            float z[N];
+            load_n<T, N>(gate + (size_t)t * gate_ld + c, z);
+#pragma unroll
+            for (int i = 0; i < N; ++i) y[i] *= act(z[i]);
+        }
+        store_n<T, N>(out + (size_t)t * out_ld + c, y);
+    };
+    const bool keep = per <= (int)blockDim.x * kKeep * N;
+    float held[kKeep][N];
     float ss = 0.0f;
-    for (int c = c0 + threadIdx.x; c < c0 + per; c += blockDim.x) {
-        const float y = value(c);
-        ss = fmaf(y, y, ss);
+    if (keep) {
+#pragma unroll
+        for (int i = 0; i < kKeep; ++i) {
+            const int c = c0 + (threadIdx.x + i * blockDim.x) * N;
+            if (c < c0 + per) {
+                value(c, held[i]);
+#pragma unroll
+                for (int e = 0; e < N; ++e) ss = fmaf(held[i][e], held[i][e], ss);
+            }
+        }
+    } else {
+        for (int c = c0 + threadIdx.x * N; c < c0 + per; c += blockDim.x * N) {
+            float y[N];
+            value(c, y);
+#pragma unroll
+            for (int e = 0; e < N; ++e) ss = fmaf(y[e], y[e], ss);
+        }
     }
     const float inv = rsqrtf(block_sum(ss, red) / (float)per + eps);
-    for (int c = c0 + threadIdx.x; c < c0 + per; c += blockDim.x) {
-        float y = value(c) * inv * w[c];
-        if (!gate_first) y *= act(Elem<T>::to_f(gate[(size_t)t * gate_ld + c]));
-        out[(size_t)t * out_ld + c] = Elem<T>::from_f(y);
+    if (keep) {
+#pragma unroll
+        for (int i = 0; i < kKeep; ++i) {
+            const int c = c0 + (threadIdx.x + i * blockDim.x) * N;
+            if (c < c0 + per) finish(c, held[i], inv);
+        }
+        return;
+    }
+    for (int c = c0 + threadIdx.x * N; c < c0 + per; c += blockDim.x * N) {
+        float y[N];
+        value(c, y);
+        finish(c, y, inv);
     }
 }
 
@@ -766,10 +816,14 @@ int launch_decay_recurrent(const float *rec, float *S, float *o, const int *seq_
 int launch_group_output(int dtype, const float *o, const float *skip, int skip_ld, const float *w, float eps, const void *gate, int gate_ld,
                         int gate_act, int gate_first, void *out, int out_ld, int tokens, int cols, int groups, cudaStream_t st) {
     if (tokens == 0) return B200_OK;
-    const int per = cols / groups, threads = per <= 64 ? 32 : (per <= 256 ? 64 : (per <= 1024 ? 128 : 256));
+    const int per = cols / groups;
+    // four columns per access when every piece of every row starts on a boundary of its access
+    const bool vec = per % 4 == 0 && cols % 4 == 0 && skip_ld % 4 == 0 && gate_ld % 4 == 0 && out_ld % 4 == 0 && aligned16(o) && aligned16(skip) && aligned16(w) &&
+                     ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(out)) & (dtype == B200_F32 ? 15 : 7)) == 0;
+    const int pieces = vec ? per / 4 : per, threads = pieces <= 64 ? 32 : (pieces <= 128 ? 64 : (pieces <= 256 ? 128 : 256));
     B200_DISPATCH_DTYPE(dtype, {
-        group_output_kernel<T><<<tokens * groups, threads, 0, st>>>(o, skip, skip_ld, w, eps, (const T *)gate, gate_ld, gate_act, gate_first, (T *)out, out_ld,
-                                                                   cols, groups);
+        auto kern = vec ? group_output_kernel<T, true> : group_output_kernel<T, false>;
+        kern<<<tokens * groups, threads, 0, st>>>(o, skip, skip_ld, w, eps, (const T *)gate, gate_ld, gate_act, gate_first, (T *)out, out_ld, cols, groups);
     });
     return cuda_status("group_output launch");
 }
