@@ -474,8 +474,9 @@ column_recurrence_kernel(const float *__restrict__ rec, int rec_ld, int q_off, i
             for (int c = 0; c < CPT; ++c) vv[c] = vs[(buf * kRecTB + tt) * CB + cl + c];
             s0 = sb[tt * TS + NV * DP], s1 = sb[tt * TS + NV * DP + 1];
         };
-        // (measured: reading ahead takes 7 % off a prompt of the decayed-memory mode and adds 6 % to the two longer token bodies)
-        constexpr bool AHEAD = MODE == 2;
+        // (measured: reading ahead takes 30 % off a prompt of the decayed-memory mode with 8 lanes or fewer; with 16 lanes, where a lane holds
+        // two pieces and the butterfly is longer, it adds 18 %, and it adds 6 % to the two longer token bodies)
+        constexpr bool AHEAD = MODE == 2 && LANES <= 8;
         float4 kc[NP], qc[NP], gc[NP];
         float v[CPT], s0c = 0.0f, s1c = 0.0f;
         if (AHEAD) load_token(0, kc, qc, gc, v, s0c, s1c);
