@@ -1016,7 +1016,7 @@ def run_silonex(args):
            "mlp": mlp}
     par = {"type": "parallel", "mixer": dict(left=dict(heads=L["heads"], kv_heads=L["kv_heads"], dim=L["dim"], vdim=L["vdim"], scale=L["dim"] ** -0.5,
                                                        softcap=50.0, mask=dict(size=L["window"]),
-                                                       rot=dict(base=5e5, dims=L["dim"], scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192))),
+                                                       rot=dict(base=5e5, dims=L["dim"], scaling=dict(factor=32.0, low=1.0, high=4.0, original=8192))),
                                              right=dict(heads=R["heads"], kv_heads=R["kv_heads"], dim=R["dim"], vdim=R["vdim"], conv=4)), "mlp": mlp}
     config = {"architecture": "Silonex", "layers": [lig, ssd, par, par], "loop": {"start": 1, "stop": 3, "times": 2}, "norm": {"eps": 1e-5},
               "streams": NS, "logit_scale": 0.5, "vocab": V, "width": W}

@@ -707,6 +707,12 @@ int b200_delta_rule_recurrent(const float *rec, float *state, float *o, const in
 int b200_mlstm_recurrent(const float *rec, float *state, float *n_state, float *m_state, float *o, float *nq, float *m_out,
                          const int *seq_start, const int *seq_pos0, const int *seq_slot, int n_seqs, int heads, int dim, int vdim,
                          b200_stream_t stream);
+/* The decayed outer-product memory with ONE decay per head and token (the recurrence of B200_MIXER_SSD and B200_MIXER_LINEAR):
+ *   S <- decay S + k v^T;  o = S^T q   (query / key head of head h: h / (heads / kv_heads)).
+ * rec: fp32 rows per token, segments padded to multiples of four floats: q | k (kv_heads*dim each) | v (heads*vdim) | skip (heads*vdim,
+ * unused here) | decay (heads).  state fp32 [num_slots, heads, dim, vdim]; o fp32 [tokens, heads*vdim]. */
+int b200_decay_recurrent(const float *rec, float *state, float *o, const int *seq_start, const int *seq_pos0, const int *seq_slot,
+                         int n_seqs, int heads, int kv_heads, int dim, int vdim, b200_stream_t stream);
 
 /* ========================================== generation loop ========================================= */
 

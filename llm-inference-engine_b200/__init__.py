@@ -212,6 +212,7 @@ SIGNATURES = {
     "b200_scored_attention_tiles_paged": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _F, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "b200_delta_rule_recurrent": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "b200_mlstm_recurrent": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "b200_decay_recurrent": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "b200_batcher_set_state_slots": [_P, _I],
     "b200_batcher_free_slots": [_P],
     "b200_batcher_set_chunk": [_P, _I],

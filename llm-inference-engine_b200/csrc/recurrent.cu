@@ -842,6 +842,13 @@ int b200_delta_rule_recurrent(const float *rec, float *state, float *o, const in
     return launch_delta_recurrent(rec, state, o, seq_start, seq_pos0, seq_slot, n_seqs, heads, kv_heads, dim, vdim, as_stream(stream), 0);
 }
 
+int b200_decay_recurrent(const float *rec, float *state, float *o, const int *seq_start, const int *seq_pos0, const int *seq_slot,
+                         int n_seqs, int heads, int kv_heads, int dim, int vdim, b200_stream_t stream) {
+    B200_REQUIRE(rec && state && o && seq_start && seq_pos0 && seq_slot, "decay_recurrent: null pointer");
+    B200_REQUIRE(n_seqs >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0, "decay_recurrent: bad shape");
+    return launch_decay_recurrent(rec, state, o, seq_start, seq_pos0, seq_slot, n_seqs, heads, kv_heads, dim, vdim, as_stream(stream), 0);
+}
+
 int b200_mlstm_recurrent(const float *rec, float *state, float *n_state, float *m_state, float *o, float *nq, float *m_out,
                          const int *seq_start, const int *seq_pos0, const int *seq_slot, int n_seqs, int heads, int dim, int vdim,
                          b200_stream_t stream) {

@@ -291,11 +291,11 @@ def _edge_case(config, W, packed, query_pos, key_pos, seen, decode, dtype="float
 
 
 EDGES = [
-    (40, 100, 61, True),      # the last key the window keeps: 39 back
-    (40, 100, 60, False),     # the first one it has dropped: 40 back
-    (40, 39, 0, True),        # the first token of the sequence, just inside
-    (40, 40, 0, False),       # ... and just outside
-    (40, 41, 1, False), (40, 41, 2, True),
+    (36, 100, 65, True),      # the last key the window keeps: 35 back
+    (36, 100, 64, False),     # the first one it has dropped: 36 back
+    (36, 35, 0, True),        # the first token of the sequence, just inside
+    (36, 36, 0, False),       # ... and just outside
+    (36, 37, 1, False), (36, 37, 2, True),
     (64, 127, 64, True), (64, 127, 63, False),     # a window edge that is a page edge
     (64, 128, 64, False), (64, 128, 65, True),
     (100, 150, 63, True), (100, 150, 64, True),    # a page edge inside the window
@@ -373,6 +373,46 @@ def test_tensor_core_attention_against_the_oracle_and_against_single_tokens(dim,
     tiles = replay(session(config, packed, dtype=dtype), reqs, [[("a", 130)], [("a", 70)]])["a"]
     single = replay(session(config, packed, dtype=dtype), reqs, [[("a", 7)]] * 28 + [[("a", 4)]])["a"]
     assert ref.rel_err(tiles, want) < 4e-2 and ref.rel_err(single, want) < 4e-2 and ref.rel_err(tiles, single) < 3e-2
+
+
+# ------------------------------------------------------------------ the recurrence's launcher alone
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 16, 12), (3, 3, 7, 5), (2, 1, 136, 20), (8, 8, 64, 64)], ids=str)
+def test_decay_recurrence_launcher_against_a_plain_loop(heads, kv_heads, dim, vdim):
+    """Three sequences in one call: one from position 0 (its slot's old state must not show), one that continues from its slot's state, a
+    single token; fp32 against a float64 loop."""
+    import ctypes as C
+
+    m = importlib.import_module("llm-inference-engine_b200")
+    pad4 = lambda n: (n + 3) & ~3
+    q0, k0 = 0, pad4(kv_heads * dim)
+    v0 = k0 + pad4(kv_heads * dim)
+    s0 = v0 + pad4(heads * vdim)
+    d0 = s0 + pad4(heads * vdim)
+    ld = d0 + pad4(heads)
+    gen = torch.Generator().manual_seed(dim)
+    lens, pos0, slots = [37, 20, 1], [0, 5, 9], [2, 0, 1]
+    T = sum(lens)
+    rec = torch.randn(T, ld, generator=gen)
+    rec[:, d0:d0 + heads] = 0.5 + 0.5 * torch.rand(T, heads, generator=gen)
+    rec[3, d0] = 1.0
+    state = torch.randn(3, heads, dim, vdim, generator=gen)
+    want_o, want_state = torch.zeros(T, heads * vdim, dtype=torch.float64), state.double().clone()
+    t = 0
+    for n, p, slot in zip(lens, pos0, slots):
+        S = torch.zeros(heads, dim, vdim, dtype=torch.float64) if p == 0 else state[slot].double().clone()
+        for _ in range(n):
+            r = rec[t].double()
+            for h in range(heads):
+                g = h // (heads // kv_heads)
+                S[h] = r[d0 + h] * S[h] + torch.outer(r[k0 + g * dim:k0 + (g + 1) * dim], r[v0 + h * vdim:v0 + (h + 1) * vdim])
+                want_o[t, h * vdim:(h + 1) * vdim] = S[h].T @ r[q0 + g * dim:q0 + (g + 1) * dim]
+            t += 1
+        want_state[slot] = S
+    d_rec, d_state, d_o = rec.to(DEV), state.to(DEV), torch.full((T, heads * vdim), float("nan"), device=DEV)
+    ints = [torch.tensor(a, dtype=torch.int32, device=DEV) for a in ([0, 37, 57, 58], pos0, slots)]
+    m.check(m.lib().b200_decay_recurrent(m.ptr(d_rec), m.ptr(d_state), m.ptr(d_o), m.ptr(ints[0]), m.ptr(ints[1]), m.ptr(ints[2]), 3, heads, kv_heads,
+                                          dim, vdim, m.stream()))
+    assert ref.rel_err(d_o.cpu(), want_o) < 1e-5 and ref.rel_err(d_state.cpu(), want_state) < 1e-5
 
 
 # ------------------------------------------------------------------ state that is carried, and state that must not be
