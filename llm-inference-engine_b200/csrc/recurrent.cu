@@ -476,7 +476,8 @@ column_recurrence_kernel(const float *__restrict__ rec, int rec_ld, int q_off, i
         };
         // (measured: reading ahead takes 30 % off a prompt of the decayed-memory mode with 8 lanes or fewer; with 16 lanes, where a lane holds
         // two pieces and the butterfly is longer, it adds 18 %, and it adds 6 % to the two longer token bodies)
-        constexpr bool AHEAD = MODE == 2 && LANES <= 8;
+        // (a lane that holds 64 rows has no registers left for a second set of pieces: it would spill)
+        constexpr bool AHEAD = MODE == 2 && LANES <= 8 && RPT <= 32;
         float4 kc[NP], qc[NP], gc[NP];
         float v[CPT], s0c = 0.0f, s1c = 0.0f;
         if (AHEAD) load_token(0, kc, qc, gc, v, s0c, s1c);

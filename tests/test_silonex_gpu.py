@@ -175,6 +175,23 @@ def test_whole_model_every_layer_fp32_and_bf16():
         assert ref.rel_err(logits16.cpu().numpy(), want.numpy()) < tol
 
 
+@pytest.mark.parametrize("width,vocab", [(36, 37), (27, 33), (50, 41)], ids=str)
+@pytest.mark.parametrize("dtype,tol", [("float32", 3e-5), ("float16", 5e-3), ("bfloat16", 3e-2)], ids=lambda v: str(v))
+def test_other_widths_and_vocabularies_in_every_dtype(width, vocab, dtype, tol):
+    """Widths and vocabularies that are no multiple of 8 (or of 2), a prompt and decoded tokens, on every engine dtype."""
+    layers = [ref.lightning_layer(heads=1, dim=5, vdim=3, decay=[0.97]), ref.mamba_layer(heads=2, vdim=9, state=8, groups=2, conv=2, norm_groups=6),
+              ref.mamba_layer(heads=2, vdim=16, state=256, groups=1, conv=4, norm_groups=1), ref.pair_layer(heads=6, kv_heads=6, dim=6, vdim=5, rot_dims=2, base=7.0, softcap=0.7),
+              ref.pair_layer(heads=2, kv_heads=1, dim=64, vdim=64, rot_dims=64, window=33, mlp=ref.dense(7))]
+    for li, layer in enumerate(layers):
+        config = ref.make_config([layer], width=width, vocab=vocab, streams=2)
+        W, packed = ref.random_model(config, seed=li)
+        toks = tokens_of(config, 100, 1)
+        sess = session(config, packed, dtype=dtype)
+        r = sess.open()
+        got = np.concatenate([sess.feed([(r, toks[:70], list(range(70)))]).cpu().numpy()] + [sess.feed([(r, [t], [0])]).cpu().numpy() for t in toks[70:]])
+        assert np.isfinite(got).all() and ref.rel_err(got, want_logits(config, W, toks)) < tol, li
+
+
 # ------------------------------------------------------------------ schedules
 def test_prefill_equals_token_by_token_decoding_and_first_tokens():
     config = ref.make_config(MIXED, loop=LOOP)
