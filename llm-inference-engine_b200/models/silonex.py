@@ -30,19 +30,26 @@ def _pkg(sub=None):
     return importlib.import_module(base + ("." + sub if sub else ""))
 
 
+def _num(d, key, default, kind=float):
+    """d[key] as a number; a key that is absent or null takes the default (the mechanism is switched off)."""
+    v = d.get(key)
+    return kind(default if v is None else v)
+
+
 def _attention_spec(m, mx):
     rot = mx.get("rot") or {}
     sc = rot.get("scaling") or {}
     mask = mx.get("mask") or {}
-    return dict(mixer=m.MIXER_ATTN_SCORED, heads=int(mx["heads"]), kv_heads=int(mx.get("kv_heads", mx["heads"])), dim=int(mx["dim"]),
-                vdim=int(mx.get("vdim", mx["dim"])), scale=float(mx["scale"]), softcap=float(mx.get("softcap", 0.0)), window=int(mask.get("size", 0)),
-                rot_dims=int(rot.get("dims", 0)), rot_base=float(rot.get("base", 10000.0)), rot_half=1, rot_factor=float(sc.get("factor", 0.0)),
-                rot_low=float(sc.get("low", 0.0)), rot_high=float(sc.get("high", 0.0)), rot_original=float(sc.get("original", 0.0)), v_norm=1,
-                attn_weight=m.ATTN_SOFTMAX, out_gate=0)
+    heads = int(mx["heads"])
+    dim = int(mx["dim"])
+    return dict(mixer=m.MIXER_ATTN_SCORED, heads=heads, kv_heads=_num(mx, "kv_heads", heads, int), dim=dim, vdim=_num(mx, "vdim", dim, int),
+                scale=float(mx["scale"]), softcap=_num(mx, "softcap", 0.0), window=_num(mask, "size", 0, int), rot_dims=_num(rot, "dims", 0, int),
+                rot_base=_num(rot, "base", 10000.0), rot_half=1, rot_factor=_num(sc, "factor", 0.0), rot_low=_num(sc, "low", 0.0),
+                rot_high=_num(sc, "high", 0.0), rot_original=_num(sc, "original", 0.0), v_norm=1, attn_weight=m.ATTN_SOFTMAX, out_gate=0)
 
 
 def _delta_spec(m, mx):
-    return dict(mixer=m.MIXER_DELTA, heads=int(mx["heads"]), kv_heads=int(mx.get("kv_heads", mx["heads"])), dim=int(mx["dim"]), vdim=int(mx["vdim"]),
+    return dict(mixer=m.MIXER_DELTA, heads=int(mx["heads"]), kv_heads=_num(mx, "kv_heads", mx["heads"], int), dim=int(mx["dim"]), vdim=int(mx["vdim"]),
                 conv=int(mx["conv"]), decay_rank=0, gate_rank=0, gate_act=1)
 
 
@@ -58,8 +65,8 @@ def layer_specs(config):
             if len(spec["decay"]) != spec["heads"]:
                 raise ValueError(f"layer {i}: {len(spec['decay'])} decays for {spec['heads']} heads")
         elif kind == "mamba2":
-            spec = dict(mixer=m.MIXER_SSD, heads=int(mx["heads"]), kv_heads=int(mx["groups"]), dim=int(mx["state"]), vdim=int(mx["vdim"]),
-                        conv=int(mx["conv"]), norm_groups=int(mx.get("norm_groups", 1)))
+            spec = dict(mixer=m.MIXER_SSD, heads=int(mx["heads"]), kv_heads=_num(mx, "groups", 1, int), dim=int(mx["state"]), vdim=int(mx["vdim"]),
+                        conv=int(mx["conv"]), norm_groups=_num(mx, "norm_groups", 1, int))
         elif kind == "parallel":
             spec = _attention_spec(m, mx["left"])
             spec.update(side=_delta_spec(m, mx["right"]), mix_scale=0.5, side_scale=0.5)
@@ -161,7 +168,7 @@ class SilonexModel:
         table = tensors["embed"].to(device=device, dtype=tdt).contiguous()  # the logits come through the embedding table itself
         self.engine = _pkg("hybrid").HybridDecoder(
             self.width, self.vocab, self.eps, specs, table, pack_ln(lambda n: tensors[n], "final.norm", device), table, tdt, device, max_tokens,
-            max_seqs, max_pages_per_seq, final_norm_kind=m.NORM_LN_PRE, loop=loop, logit_scale=float(config.get("logit_scale", 1.0)), streams=streams)
+            max_seqs, max_pages_per_seq, final_norm_kind=m.NORM_LN_PRE, loop=loop, logit_scale=_num(config, "logit_scale", 1.0), streams=streams)
 
     @classmethod
     def from_pretrained(cls, model_dir, config, dtype="bfloat16", device="cuda:0", **limits):

@@ -42,6 +42,34 @@ def test_layer_specs_follow_the_configuration():
         f.layer_specs(ref.make_config([ref.lightning_layer(heads=2, decay=[0.5])]))
 
 
+def test_layer_specs_switch_off_what_is_absent_or_null():
+    m = b200()
+    f = importlib.import_module("llm-inference-engine_b200.models.silonex")
+    pair = ref.pair_layer(heads=6, kv_heads=3, dim=10, vdim=14, r_heads=2, r_kv_heads=2, r_dim=6, r_vdim=4, conv=2)
+    left, right = pair["mixer"]["left"], pair["mixer"]["right"]
+    for absent in (False, True):  # the keys left out, then present with null
+        for key in ("mask", "rot", "softcap", "kv_heads", "vdim"):
+            if absent:
+                left.pop(key, None)
+            else:
+                left[key] = None
+        if absent:
+            right.pop("kv_heads", None)
+        else:
+            right["kv_heads"] = None
+        mamba = ref.mamba_layer(heads=4, vdim=6, state=10, groups=2, conv=3, norm_groups=3)
+        if absent:
+            del mamba["mixer"]["norm_groups"], mamba["mixer"]["groups"]
+        else:
+            mamba["mixer"]["norm_groups"] = mamba["mixer"]["groups"] = None
+        c, b = f.layer_specs(ref.make_config([pair, mamba]))
+        assert (c["window"], c["rot_dims"], c["softcap"], c["rot_factor"], c["kv_heads"], c["vdim"]) == (0, 0, 0.0, 0.0, 6, 10)
+        assert c["side"]["kv_heads"] == 2 and (b["norm_groups"], b["kv_heads"]) == (1, 1)
+    left["rot"] = {"dims": 4, "base": 50.0, "scaling": None}  # rotation without slowed wavelengths
+    c = f.layer_specs(ref.make_config([pair]))[0]
+    assert (c["rot_dims"], c["rot_base"], c["rot_factor"], c["mixer"]) == (4, 50.0, 0.0, m.MIXER_ATTN_SCORED)
+
+
 def test_oracle_run_order_of_looped_blocks():
     assert ref.run_order(ref.make_config([0] * 4)) == [0, 1, 2, 3]
     assert ref.run_order(ref.make_config([0] * 4, loop=(1, 3, 2))) == [0, 1, 2, 1, 2, 3]

@@ -84,6 +84,13 @@ MIXED = [ref.lightning_layer(mlp=ref.dense()), ref.mamba_layer(mlp=ref.dense(24)
 LOOP = (1, 4, 3)
 
 
+def _bare_pair():
+    """The windowed attention with its window, rotation and cap named null: every key since the start is seen, as it is."""
+    layer = ref.pair_layer(heads=2, kv_heads=2, dim=20, vdim=8, r_heads=2, r_kv_heads=1)
+    layer["mixer"]["left"].update(mask=None, rot=None, softcap=None)
+    return layer
+
+
 # ------------------------------------------------------------------ each mechanism alone (one-layer models, residual stream compared)
 @pytest.mark.parametrize("layer", [
     ref.lightning_layer(),
@@ -102,8 +109,9 @@ LOOP = (1, 4, 3)
     ref.pair_layer(heads=6, kv_heads=6, dim=6, vdim=5, rot_dims=2, base=7.0, softcap=0.7),       # a cap that binds; odd sizes
     ref.pair_layer(window=64, r_heads=2, r_kv_heads=1, r_dim=144, r_vdim=8),
     ref.pair_layer(scaling={"factor": 32.0, "low": 2.0, "high": 3.0, "original": 40}, mlp=ref.dense(7)),
+    _bare_pair(),
 ], ids=["lightning", "lightning_tiny", "lightning_wide", "lightning_long_keys", "mamba", "mamba_tiny", "mamba_groups", "mamba_norm_heads",
-        "mamba_norm_cuts", "pair", "pair_sizes", "pair_window_1", "pair_never_binds", "pair_odd", "pair_long_keys", "pair_scaling"])
+        "mamba_norm_cuts", "pair", "pair_sizes", "pair_window_1", "pair_never_binds", "pair_odd", "pair_long_keys", "pair_scaling", "pair_bare"])
 @pytest.mark.parametrize("streams", [3, 0], ids=["streams3", "plain"])
 def test_one_layer_residual_stream(layer, streams):
     config = ref.make_config([layer], streams=streams)
