@@ -292,7 +292,7 @@ def _windowed_model(window, seed, dim=32, vdim=12, rot_dims=8, scale=0.3, softca
     return config, W, packed
 
 
-def _edge_case(config, W, packed, query_pos, key_pos, seen, decode, dtype="float32", tol=3e-5):
+def _edge_case(config, W, packed, query_pos, key_pos, seen, decode, dtype="float32", tol=3e-5, pool_tokens=512):
     plain = [t for t in tokens_of(config, 3 * (query_pos + 1), query_pos * 1000 + key_pos) if t not in (KEY_TOKEN, QUERY_TOKEN)][:query_pos + 1]
     with_key, without = list(plain), list(plain)
     with_key[query_pos] = without[query_pos] = QUERY_TOKEN
@@ -304,7 +304,7 @@ def _edge_case(config, W, packed, query_pos, key_pos, seen, decode, dtype="float
     changed = ref.rel_err(want_without, want)
     assert changed > 1e-2 if seen else changed == 0.0, changed
     for sequence, expect in ((with_key, want), (without, want_without)):
-        sess = session(config, packed, dtype=dtype)
+        sess = session(config, packed, dtype=dtype, pool_tokens=pool_tokens, max_batch_tokens=pool_tokens)
         r = sess.open()
         if decode and query_pos > 0:   # everything before the query is in the pool already; it arrives alone
             sess.feed([(r, sequence[:query_pos], [])])
@@ -343,6 +343,18 @@ def test_window_edges_with_a_dominant_key(window, query_pos, key_pos, seen, deco
 def test_tensor_core_window_edges_with_a_dominant_key(window, query_pos, key_pos, seen, decode):
     config, W, packed = _windowed_model(window, seed=window + 2, dim=64, vdim=32, rot_dims=16, scale=0.25)
     _edge_case(config, W, packed, query_pos, key_pos, seen, decode, dtype="bfloat16", tol=3e-2)
+
+
+# a window of hundreds of keys over a dozen pages: the per-token kernel takes its widest CTA there, the tiles walk many key blocks
+LONG_EDGES = [(600, 700, 101, True), (600, 700, 100, False)]
+
+
+@pytest.mark.parametrize("decode", [False, True], ids=["prompt", "decoded"])
+@pytest.mark.parametrize("window,query_pos,key_pos,seen", LONG_EDGES, ids=lambda v: str(v))
+@pytest.mark.parametrize("dtype,tol,sizes", [("float32", 3e-5, {}), ("bfloat16", 3e-2, dict(dim=64, vdim=32, rot_dims=16, scale=0.25))], ids=["fp32", "tiles"])
+def test_edges_of_a_window_of_hundreds_of_keys(dtype, tol, sizes, window, query_pos, key_pos, seen, decode):
+    config, W, packed = _windowed_model(window, seed=window + 3, **sizes)
+    _edge_case(config, W, packed, query_pos, key_pos, seen, decode, dtype=dtype, tol=tol, pool_tokens=768)
 
 
 def _far_model(kind, seed):
